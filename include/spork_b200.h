@@ -1,0 +1,123 @@
+/* C ABI of libspork_b200: hand-written sm_100a (B200) kernels behind the launch
+ * interface of the akeley98/spork GEMM/attention testbed.
+ *
+ * Conventions shared by every entry point (they mirror the reference's launch
+ * functions, gemm/gemm_sm90.h:14, gemm/gemm_sm80.h:5-6, gemm/gemm_baseline.h:5):
+ *   - the caller owns every buffer; pointers are DEVICE pointers unless the
+ *     name says "htod" (host in, host out);
+ *   - launches are asynchronous on the caller's stream and never synchronise;
+ *   - `stream` is a cudaStream_t passed as void* so that this header needs no
+ *     CUDA include;
+ *   - return value 0 = success; a positive value below 10000 is a cudaError_t;
+ *     values >= SPORK_ERR_BASE are this library's own codes (below).
+ * Unlike the reference (which asserts and prints), argument errors are
+ * returned, never trapped.
+ */
+#ifndef SPORK_B200_H
+#define SPORK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Every entry point is exported; everything else in the library is hidden. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define SPORK_ERR_BASE 10000
+#define SPORK_ERR_BAD_ARGUMENT 10001   /* null / misaligned pointer, unknown variant */
+#define SPORK_ERR_UNSUPPORTED_SHAPE 10002 /* see spork_gemm_sm100_supports */
+#define SPORK_ERR_NO_SM100 10003       /* current device is not compute capability 10.x */
+#define SPORK_ERR_DRIVER 10004         /* tensor-map encode or driver entry point failed */
+#define SPORK_ERR_DEVICE_TIMEOUT 10005 /* a bounded device-side wait ran out (status word set) */
+#define SPORK_ERR_TOO_LARGE 10006      /* beyond a stated fixed capacity */
+
+/* ---- GEMM: C[M,N] (fp32, row-major) = A[M,K] (fp16, row-major) . B[N,K]^T (fp16, row-major) ----
+ * Operand layout of the reference harness's hot call
+ * `GPU_Tensors{M,N,K,d_a,d_bCol,d_c,0,1,0}` (gemm/gemm_test.cu:305,365), with
+ * fp16 inputs and fp32 accumulation/output instead of fp32/TF32. */
+
+/* 1 if (M,N,K) can be launched: K % 8 == 0 (a row of A or B must be a multiple
+ * of 16 bytes for TMA), everything else arbitrary (ragged M, N, K are
+ * handled; M, N or K == 0 is legal).  Replaces matmul_sm80_supports
+ * (gemm/gemm_sm80.h:6) / the asserts of gemm/gemm_sm90.cu:1269-1276. */
+int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K);
+
+/* Launch.  variant: 0 = choose, 64 / 128 / 256 = width of the output tile
+ * along N (the n64/n128/n256 variants of xgemm_Sm90_n{64,128,256}.py).
+ * Replaces matmul_sm90(t, gemm_sm90_k_mode::output_stationary, stream)
+ * (gemm/gemm_sm90.cu:1344-1360). */
+int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int variant,
+                            void* stream);
+
+/* Launch with every tunable explicit (benchmark sweeps and tests).
+ *   block_n   64 / 128 / 256   output-tile width
+ *   cta_group 1 = one CTA per tile (128 x block_n),
+ *             2 = a CTA pair per tile (256 x block_n, tcgen05 cta_group::2)
+ *   split_k   >= 1: K is cut into split_k ranges whose partial products are
+ *             added into C with TMA reduce-add (C is zeroed first); the
+ *             counterpart of gemm_sm90_k_mode::split_k_outer
+ *             (gemm/gemm_sm90.h:8, gemm/gemm_sm90.cu:1096-1114)
+ *   max_ctas  0 = one CTA per SM, else an upper bound on the grid. */
+int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
+                               int block_n, int cta_group, int split_k, int max_ctas, void* stream);
+
+/* Synchronises `stream`, then returns and clears the device status word of the
+ * current device: 0, or SPORK_ERR_DEVICE_TIMEOUT if a kernel abandoned a
+ * bounded wait (detail word through *detail when non-null).  Replaces the
+ * reference's cudaGetLastError polling (gemm/gemm_test.cu:474-477). */
+int spork_gemm_sm100_status(void* stream, uint32_t* detail);
+
+/* Host-buffer convenience (the htod_f32_* pattern of tk_4090_fwd.hpp:7): copies
+ * A and B to the device, runs the GEMM, copies C back and synchronises.  Device
+ * staging buffers are allocated on first use and kept. */
+int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* hA, const void* hB, float* hC);
+
+/* ---- Harness kernels (gemm/gemm_test.cu) --------------------------------- */
+
+/* Seeded fixture fill of a rows x cols fp16 matrix; code: 0 sparse random,
+ * 1 identity, 2 tiled numbers (gemm/gemm_test.cu:55-96), 3 uniform [-1,1),
+ * 4 unit normal.  transpose_rule as in the reference. */
+int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
+                             int transpose_rule, void* stream);
+
+/* The reference's oracle kernel restated for fp16 inputs: fp32 FFMA, k
+ * ascending (gemm/gemm_baseline.cu:19-168).  Same operand layout as above. */
+int spork_gemm_baseline_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
+                               void* stream);
+
+/* Element-wise comparison of two rows x cols fp32 matrices on the device.
+ * out[0] = packed (row << 32 | col) of the first element failing the
+ * reference's sign + ratio rule (gemm/gemm_test.cu:131-154), UINT64_MAX if
+ * none; out[1] = bit pattern of max |a - b| as a double.  `d_out` is a device
+ * buffer of two uint64. */
+int spork_compare_f32(const float* d_a, const float* d_b, uint32_t rows, uint32_t cols, uint64_t* d_out,
+                      void* stream);
+
+/* ---- Attention forward ---------------------------------------------------
+ * O = softmax(Q K^T * scale) V per head; q, k, v, o are [BH][S][D] fp16,
+ * row-major, each head laid out like the reference's single (N, d) problem
+ * (matrix_util.hpp:40-45); softmax in fp32.  Replaces
+ * launch_tk_4090_fwd_kernel (tk_4090_fwd.hpp:5). */
+int spork_attn_sm100_supports(int BH, int S, int D);
+int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
+                             void* stream);
+
+/* Reference-shaped FFI entry (tk_4090_fwd.hpp:7, called from
+ * torch_attn.py:40-57): HOST fp32 (N, d) arrays, one head, scale 1/sqrt(d). */
+void htod_f32_attn_sm100_fwd(int N, int d, const float* q, const float* k, const float* v, float* o);
+
+/* Library/build information: "spork_b200 <version> sm_100a". */
+const char* spork_b200_version(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPORK_B200_H */

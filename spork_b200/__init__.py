@@ -1,0 +1,23 @@
+"""spork_b200: hand-written sm_100a (B200) GEMM and attention kernels behind the
+launch interface of the akeley98/spork testbed.
+
+The product is ``libspork_b200.so`` (a C-ABI library, ``include/spork_b200.h``).
+This package is the Python face of it: ``spork_b200.api`` binds the C ABI with
+ctypes and accepts torch tensors (torch is used for device memory and streams
+only).  There is no CPU fallback: every call raises if the library is missing
+or the device is not a B200-class GPU.
+"""
+from .api import (  # noqa: F401
+    SporkError,
+    attn_fwd,
+    compare_f32,
+    gemm_baseline,
+    init_test_data,
+    lib,
+    library_path,
+    matmul_sm100,
+    matmul_sm100_htod,
+    matmul_sm100_supports,
+    status,
+    version,
+)

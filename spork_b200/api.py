@@ -1,0 +1,231 @@
+"""ctypes binding of ``libspork_b200.so`` for torch tensors.
+
+Function names follow the reference's launch functions (``matmul_sm90`` /
+``matmul_sm80_supports`` / ``matmul_baseline`` in gemm/gemm_sm90.h:14,
+gemm/gemm_sm80.h:5-6, gemm/gemm_baseline.h:5); argument meaning is that of the
+harness's hot call ``GPU_Tensors{M,N,K,d_a,d_bCol,d_c,0,1,0}``
+(gemm/gemm_test.cu:365): ``a`` is (M, K), ``b`` is (N, K), both fp16 and
+contiguous; ``c`` is (M, N) fp32.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import struct
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libspork_b200.so")
+
+ERR_BASE = 10000
+_ERR_NAMES = {
+    10001: "bad argument (null or misaligned pointer, unknown variant)",
+    10002: "unsupported shape (K must be a multiple of 8)",
+    10003: "current device is not an sm_100 (B200-class) GPU",
+    10004: "driver call failed (tensor map encode)",
+    10005: "a bounded device-side wait ran out",
+    10006: "size beyond the fixed capacity of this entry point",
+}
+
+
+class SporkError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        detail = _ERR_NAMES.get(code, f"cudaError_t {code}" if code < ERR_BASE else "unknown")
+        super().__init__(f"{what} failed with code {code}: {detail}")
+
+
+def library_path() -> str:
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the C-ABI library; raises (never falls back) if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise FileNotFoundError(
+                f"{_LIB_PATH} is missing: build it with `python -m spork_b200.build` (needs nvcc); "
+                "there is no CPU fallback")
+        L = ctypes.CDLL(_LIB_PATH)
+        u32, i32, vp = ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p
+        L.spork_gemm_sm100_supports.argtypes = [u32, u32, u32]
+        L.spork_gemm_sm100_supports.restype = i32
+        L.spork_gemm_sm100_f16f32.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
+        L.spork_gemm_sm100_f16f32.restype = i32
+        L.spork_gemm_sm100_f16f32_ex.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, i32, i32, vp]
+        L.spork_gemm_sm100_f16f32_ex.restype = i32
+        L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]
+        L.spork_gemm_sm100_status.restype = i32
+        L.spork_gemm_sm100_htod_f16f32.argtypes = [u32, u32, u32, vp, vp, vp]
+        L.spork_gemm_sm100_htod_f16f32.restype = i32
+        L.spork_init_test_data_f16.argtypes = [vp, u32, u32, i32, u32, i32, vp]
+        L.spork_init_test_data_f16.restype = i32
+        L.spork_gemm_baseline_f16f32.argtypes = [u32, u32, u32, vp, vp, vp, vp]
+        L.spork_gemm_baseline_f16f32.restype = i32
+        L.spork_compare_f32.argtypes = [vp, vp, u32, u32, vp, vp]
+        L.spork_compare_f32.restype = i32
+        if hasattr(L, "spork_attn_sm100_fwd_f16"):
+            L.spork_attn_sm100_supports.argtypes = [i32, i32, i32]
+            L.spork_attn_sm100_supports.restype = i32
+            L.spork_attn_sm100_fwd_f16.argtypes = [i32, i32, i32, vp, vp, vp, vp, ctypes.c_float, vp]
+            L.spork_attn_sm100_fwd_f16.restype = i32
+            L.htod_f32_attn_sm100_fwd.argtypes = [i32, i32, vp, vp, vp, vp]
+            L.htod_f32_attn_sm100_fwd.restype = None
+        L.spork_b200_version.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def version() -> str:
+    return lib().spork_b200_version().decode()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise SporkError(rc, what)
+
+
+def _stream_ptr(stream) -> int:
+    import torch
+
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream)
+
+
+def _dev_ptr(t, dtype, what: str) -> int:
+    import torch
+
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{what} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{what} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    return int(t.data_ptr())
+
+
+def matmul_sm100_supports(M: int, N: int, K: int) -> bool:
+    return bool(lib().spork_gemm_sm100_supports(M, N, K))
+
+
+def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, cta_group: int | None = None,
+                 split_k: int = 1, max_ctas: int = 0, stream=None):
+    """c[M,N] (fp32) = a[M,K] (fp16) @ b[N,K]^T (fp16); asynchronous on ``stream``.
+
+    ``variant`` 0/64/128/256 picks the output-tile width like the reference's
+    n64/n128/n256 kernels.  ``block_n``/``cta_group``/``split_k``/``max_ctas``
+    select the explicit-tunables entry point instead.
+    """
+    import torch
+
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if c is None:
+        c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    if tuple(c.shape) != (M, N):
+        raise ValueError(f"c must be {(M, N)}, got {tuple(c.shape)}")
+    pa = _dev_ptr(a, torch.float16, "a")
+    pb = _dev_ptr(b, torch.float16, "b")
+    pc = _dev_ptr(c, torch.float32, "c")
+    with torch.cuda.device(a.device):
+        sp = _stream_ptr(stream)
+        if block_n is None and cta_group is None and split_k == 1 and max_ctas == 0:
+            rc = lib().spork_gemm_sm100_f16f32(M, N, K, pa, pb, pc, variant, sp)
+        else:
+            bn = block_n if block_n is not None else (variant or (64 if N <= 64 else 128 if N <= 128 else 256))
+            rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cta_group or 2, split_k, max_ctas, sp)
+    _check(rc, "spork_gemm_sm100_f16f32")
+    return c
+
+
+def status(stream=None, device=None) -> None:
+    """Synchronise ``stream`` and raise SporkError if a kernel reported a device-side timeout."""
+    import torch
+
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        detail = ctypes.c_uint32(0)
+        rc = lib().spork_gemm_sm100_status(_stream_ptr(stream), ctypes.byref(detail))
+    if rc != 0:
+        raise SporkError(rc, f"device status (detail 0x{detail.value:08x})")
+
+
+def matmul_sm100_htod(a_host, b_host, c_host=None):
+    """Host-buffer GEMM: fp16 CPU tensors in, fp32 CPU tensor out (copies inside the call)."""
+    import torch
+
+    M, K = a_host.shape
+    N, _ = b_host.shape
+    if c_host is None:
+        c_host = torch.empty((M, N), dtype=torch.float32)
+    for t, dt in ((a_host, torch.float16), (b_host, torch.float16), (c_host, torch.float32)):
+        if t.is_cuda or t.dtype != dt or not t.is_contiguous():
+            raise TypeError("host tensors must be contiguous CPU tensors (fp16, fp16, fp32)")
+    rc = lib().spork_gemm_sm100_htod_f16f32(M, N, K, a_host.data_ptr(), b_host.data_ptr(), c_host.data_ptr())
+    _check(rc, "spork_gemm_sm100_htod_f16f32")
+    return c_host
+
+
+def init_test_data(t, code: int, seed: int = 0, transpose_rule: bool = False, stream=None):
+    """Fill the 2-D fp16 CUDA tensor ``t`` with fixture ``code`` (gemm/gemm_test.cu:55-96 plus codes 3, 4)."""
+    import torch
+
+    rows, cols = t.shape
+    with torch.cuda.device(t.device):
+        rc = lib().spork_init_test_data_f16(_dev_ptr(t, torch.float16, "t"), rows, cols, code, seed & 0xFFFFFFFF,
+                                            int(transpose_rule), _stream_ptr(stream))
+    _check(rc, "spork_init_test_data_f16")
+    return t
+
+
+def gemm_baseline(a, b, c=None, stream=None):
+    """The slow CUDA-core comparison GEMM (same operand layout as matmul_sm100)."""
+    import torch
+
+    M, K = a.shape
+    N, _ = b.shape
+    if c is None:
+        c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib().spork_gemm_baseline_f16f32(M, N, K, _dev_ptr(a, torch.float16, "a"), _dev_ptr(b, torch.float16, "b"),
+                                              _dev_ptr(c, torch.float32, "c"), _stream_ptr(stream))
+    _check(rc, "spork_gemm_baseline_f16f32")
+    return c
+
+
+def compare_f32(x, y, stream=None):
+    """On-device comparison; returns (first_failure or None, max_abs_diff) like the reference's comparator."""
+    import torch
+
+    rows, cols = x.shape
+    out = torch.empty(2, dtype=torch.int64, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().spork_compare_f32(_dev_ptr(x, torch.float32, "x"), _dev_ptr(y, torch.float32, "y"), rows, cols,
+                                     int(out.data_ptr()), _stream_ptr(stream))
+    _check(rc, "spork_compare_f32")
+    packed, diff_bits = (int(v) & 0xFFFFFFFFFFFFFFFF for v in out.cpu().tolist())
+    first = None if packed == 0xFFFFFFFFFFFFFFFF else (packed >> 32, packed & 0xFFFFFFFF)
+    max_diff = struct.unpack("<d", struct.pack("<Q", diff_bits))[0]
+    return first, max_diff
+
+
+def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None):
+    """o = softmax(q k^T scale) v per head; q, k, v are (BH, S, D) fp16 CUDA tensors."""
+    import torch
+
+    BH, S, D = q.shape
+    if o is None:
+        o = torch.empty_like(q)
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    with torch.cuda.device(q.device):
+        rc = lib().spork_attn_sm100_fwd_f16(BH, S, D, _dev_ptr(q, torch.float16, "q"), _dev_ptr(k, torch.float16, "k"),
+                                            _dev_ptr(v, torch.float16, "v"), _dev_ptr(o, torch.float16, "o"),
+                                            ctypes.c_float(scale), _stream_ptr(stream))
+    _check(rc, "spork_attn_sm100_fwd_f16")
+    return o

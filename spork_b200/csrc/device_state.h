@@ -1,0 +1,38 @@
+// Per-device state shared by the kernels of this library: SM count, the device
+// status word that bounded waits report into, and cached staging buffers of
+// the host-buffer entry points.  One slot per device ordinal, created on first
+// use with that device current, so that host threads driving different GPUs
+// (one per GPU in the M-sharded runs) never share mutable state.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+// CTA-pair (tcgen05 cta_group::2) kernels are the default GEMM path.
+#ifndef SPORK_DEFAULT_CTA_GROUP
+#define SPORK_DEFAULT_CTA_GROUP 2
+#endif
+
+namespace spork {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    int ordinal = -1;
+    int sm_count = 0;
+    int cc_major = 0;
+    uint32_t* status_word = nullptr;  // device memory, zero = healthy
+    // Staging buffers of the htod entry points (grown on demand, never shrunk).
+    void* staging[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t staging_bytes[4] = {0, 0, 0, 0};
+};
+
+// State of the CURRENT device; creates it on first use.  Returns 0 or an error
+// code (SPORK_ERR_NO_SM100 when the device is not compute capability 10.x).
+int current_device_state(DeviceState** out);
+
+// Grow staging buffer `slot` of `dev` to at least `bytes`; returns 0 or a cudaError_t.
+int ensure_staging(DeviceState& dev, int slot, size_t bytes);
+
+}  // namespace spork

@@ -1,0 +1,288 @@
+// Device-side harness pieces that surround the GEMM in the reference's
+// benchmark/correctness driver (gemm/gemm_test.cu): seeded fixture fill, the
+// slow CUDA-core GEMM every algorithm is compared against, and the on-device
+// comparison.  fp16 operands, fp32 results.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/spork_b200.h"
+#include "device_state.h"
+
+namespace spork {
+namespace harness {
+
+// The position hash of gemm/gemm_test.cu:34-53 (PCG3D folded to 64 bits).
+__host__ __device__ inline uint64_t pcg3d(uint32_t x, uint32_t y, uint32_t z)
+{
+    x = x * 1664525u + 1013904223u;
+    y = y * 1664525u + 1013904223u;
+    z = z * 1664525u + 1013904223u;
+    x += y * z;
+    y += z * x;
+    z += x * y;
+    x ^= x >> 16u;
+    y ^= y >> 16u;
+    z ^= z >> 16u;
+    x += y * z;
+    y += z * x;
+    z += x * y;
+    return x ^ (uint64_t(y) << 12u) ^ (uint64_t(z) << 24u);
+}
+
+// Fixture element at logical coordinate (x, y).  Codes 0..2 are the
+// reference's three (gemm/gemm_test.cu:66-91) rounded once to fp16; 3 is
+// uniform [-1,1) from 24 hashed bits; 4 is a unit normal built as the
+// Irwin-Hall sum of twelve hashed uniforms, integer arithmetic throughout so
+// the host generator reproduces it bit for bit.
+__device__ inline __half fixture_value(uint32_t x, uint32_t y, int code, uint32_t seed)
+{
+    switch (code) {
+    case 1:
+        return __float2half_rn(x == y ? 1.0f : 0.0f);
+    case 2:
+        return __float2half_rn(float((x % 64u) + 100u * (y % 64u)));
+    case 3: {
+        const uint32_t bits = uint32_t(pcg3d(x, y, seed) & 0xFFFFFFu);
+        return __float2half_rn(__fsub_rn(__fmul_rn(float(bits), 1.0f / 8388608.0f), 1.0f));
+    }
+    case 4: {
+        uint32_t sum = 0;
+        for (uint32_t i = 0; i < 12u; ++i) {
+            sum += uint32_t(pcg3d(x, y, seed + 0x9E3779B9u * i) & 0xFFFFFFu);
+        }
+        const double v = (double(sum) - 6.0 * 16777216.0) * (1.0 / 16777216.0);
+        return __float2half_rn(float(v));
+    }
+    default: {
+        const uint64_t randbits = pcg3d(x, y, 20010106u);
+        if (randbits % 100000u == 0) {
+            return __float2half_rn(1000.0f);
+        }
+        if (randbits % 4u != 0u) {
+            return __float2half_rn(0.0f);
+        }
+        float v = __fmul_rn(float(pcg3d(x, y, 19980724u) % 1000000u), 1e-6f);
+        v = __fmul_rn(__fmul_rn(v, v), __fmul_rn(v, v));
+        return __float2half_rn(v);
+    }
+    }
+}
+
+__global__ void init_test_data_kernel(__half* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
+                                      bool transpose_rule)
+{
+    const uint32_t tid_x = threadIdx.x + blockIdx.x * blockDim.x;
+    const uint32_t tid_y = threadIdx.y + blockIdx.y * blockDim.y;
+    for (uint32_t r = tid_y; r < rows; r += blockDim.y * gridDim.y) {
+        for (uint32_t c = tid_x; c < cols; c += blockDim.x * gridDim.x) {
+            const uint32_t x = transpose_rule ? r : c;
+            const uint32_t y = transpose_rule ? c : r;
+            d_tensor[size_t(r) * cols + c] = fixture_value(x, y, code, seed);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Comparison GEMM: what gemm/gemm_baseline.cu computes (fp32 FFMA, k strictly
+// ascending per output element, predicated edges), for fp16 operands in the
+// layout A[M,K], B[N,K].  One thread per output element inside a 64x64 tile
+// staged through shared memory 32 k at a time; slow by design.
+constexpr int kTile = 64;
+constexpr int kTileK = 32;
+
+__global__ void __launch_bounds__(256) baseline_kernel(uint32_t M, uint32_t N, uint32_t K, const __half* A,
+                                                       const __half* B, float* C)
+{
+    __shared__ float sa[kTile][kTileK + 1];
+    __shared__ float sb[kTile][kTileK + 1];
+    const uint32_t tiles_n = (N + kTile - 1) / kTile;
+    const uint32_t tiles_m = (M + kTile - 1) / kTile;
+    for (uint32_t t = blockIdx.x; t < tiles_m * tiles_n; t += gridDim.x) {
+        const uint32_t m0 = (t / tiles_n) * kTile;
+        const uint32_t n0 = (t % tiles_n) * kTile;
+        const uint32_t tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
+        float acc[4][4] = {};
+        for (uint32_t k0 = 0; k0 < K; k0 += kTileK) {
+            for (uint32_t i = threadIdx.x; i < kTile * kTileK; i += blockDim.x) {
+                const uint32_t r = i / kTileK, kk = i % kTileK;
+                const uint32_t k = k0 + kk;
+                sa[r][kk] = (m0 + r < M && k < K) ? __half2float(A[size_t(m0 + r) * K + k]) : 0.0f;
+                sb[r][kk] = (n0 + r < N && k < K) ? __half2float(B[size_t(n0 + r) * K + k]) : 0.0f;
+            }
+            __syncthreads();
+            for (uint32_t kk = 0; kk < kTileK; ++kk) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[i][j] = __fmaf_rn(sa[ty * 4 + i][kk], sb[tx * 4 + j][kk], acc[i][j]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        for (int i = 0; i < 4; ++i) {
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+                if (m < M && n < N) {
+                    C[size_t(m) * N + n] = acc[i][j];
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Comparator: the sign + ratio rule of gemm/gemm_test.cu:131-154 with the first
+// failing coordinate found by a 64-bit atomicMin, plus the largest absolute
+// difference (fp64 bit pattern, ordered as an unsigned integer because it is
+// non-negative).
+__global__ void compare_init_kernel(unsigned long long* out)
+{
+    out[0] = ~0ull;
+    out[1] = 0ull;
+}
+
+__global__ void compare_kernel(const float* a_mat, const float* b_mat, uint32_t rows, uint32_t cols,
+                               unsigned long long* out)
+{
+    const uint32_t tid_x = threadIdx.x + blockIdx.x * blockDim.x;
+    const uint32_t tid_y = threadIdx.y + blockIdx.y * blockDim.y;
+    double worst = 0.0;
+    for (uint32_t y = tid_y; y < rows; y += blockDim.y * gridDim.y) {
+        for (uint32_t x = tid_x; x < cols; x += blockDim.x * gridDim.x) {
+            float a = a_mat[size_t(y) * cols + x];
+            float b = b_mat[size_t(y) * cols + x];
+            const double d = fabs(double(a) - double(b));
+            worst = (d > worst || d != d) ? d : worst;
+            bool correct = a * b >= 0.0f;
+            if (correct) {
+                a = fabsf(a);
+                b = fabsf(b);
+                const float lo = fminf(a, b);
+                const float hi = fmaxf(a, b);
+                correct = hi == 0 || hi / lo < (1.0f + 1 / 32.0f);
+            }
+            if (!correct) {
+                atomicMin(&out[0], (unsigned long long)(uint64_t(y) << 32u | x));
+            }
+        }
+    }
+    if (worst != worst) {
+        worst = __longlong_as_double(0x7FF0000000000000ll);  // NaN difference reported as +inf
+    }
+    if (worst > 0.0) {
+        atomicMax(&out[1], (unsigned long long)__double_as_longlong(worst));
+    }
+}
+
+}  // namespace harness
+}  // namespace spork
+
+extern "C" int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
+                                        int transpose_rule, void* stream)
+{
+    if (rows == 0 || cols == 0) {
+        return 0;
+    }
+    if (!d_tensor || code < 0 || code > 4) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    dim3 block{16, 16, 1};
+    dim3 grid{(cols + 15u) / 16u, (rows + 15u) / 16u, 1};
+    if (grid.x > 4096) {
+        grid.x = 4096;
+    }
+    if (grid.y > 4096) {
+        grid.y = 4096;
+    }
+    spork::harness::init_test_data_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half*>(d_tensor), rows, cols, code, seed, transpose_rule != 0);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int spork_gemm_baseline_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
+                                          void* stream)
+{
+    if (M == 0 || N == 0) {
+        return 0;
+    }
+    if (!C || (K != 0 && (!A || !B))) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    const uint64_t tiles = uint64_t((M + 63) / 64) * ((N + 63) / 64);
+    const unsigned grid = tiles < 148u * 8u ? unsigned(tiles) : 148u * 8u;
+    spork::harness::baseline_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        M, N, K, static_cast<const __half*>(A), static_cast<const __half*>(B), C);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int spork_compare_f32(const float* d_a, const float* d_b, uint32_t rows, uint32_t cols, uint64_t* d_out,
+                                 void* stream)
+{
+    if (!d_out || ((rows != 0 && cols != 0) && (!d_a || !d_b))) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    auto* out = reinterpret_cast<unsigned long long*>(d_out);
+    spork::harness::compare_init_kernel<<<1, 1, 0, s>>>(out);
+    if (rows != 0 && cols != 0) {
+        dim3 block{16, 16, 1};
+        dim3 grid{(cols + 15u) / 16u, (rows + 15u) / 16u, 1};
+        if (grid.x > 1024) {
+            grid.x = 1024;
+        }
+        if (grid.y > 1024) {
+            grid.y = 1024;
+        }
+        spork::harness::compare_kernel<<<grid, block, 0, s>>>(d_a, d_b, rows, cols, out);
+    }
+    return (int)cudaGetLastError();
+}
+
+extern "C" int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* hA, const void* hB,
+                                            float* hC)
+{
+    if (!spork_gemm_sm100_supports(M, N, K)) {
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    if (M == 0 || N == 0) {
+        return 0;
+    }
+    if (!hC || (K != 0 && (!hA || !hB))) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::DeviceState* dev = nullptr;
+    int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    const size_t a_bytes = size_t(M) * K * 2, b_bytes = size_t(N) * K * 2, c_bytes = size_t(M) * N * 4;
+    if ((rc = spork::ensure_staging(*dev, 0, a_bytes ? a_bytes : 16)) != 0 ||
+        (rc = spork::ensure_staging(*dev, 1, b_bytes ? b_bytes : 16)) != 0 ||
+        (rc = spork::ensure_staging(*dev, 2, c_bytes)) != 0) {
+        return rc;
+    }
+    cudaStream_t s = cudaStreamPerThread;
+    cudaError_t e = cudaSuccess;
+    if (K != 0) {
+        e = cudaMemcpyAsync(dev->staging[0], hA, a_bytes, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(dev->staging[1], hB, b_bytes, cudaMemcpyHostToDevice, s);
+        }
+        if (e != cudaSuccess) {
+            return (int)e;
+        }
+    }
+    rc = spork_gemm_sm100_f16f32(M, N, K, dev->staging[0], dev->staging[1], static_cast<float*>(dev->staging[2]), 0,
+                                 s);
+    if (rc) {
+        return rc;
+    }
+    e = cudaMemcpyAsync(hC, dev->staging[2], c_bytes, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) {
+        return (int)e;
+    }
+    return spork_gemm_sm100_status(s, nullptr);
+}
