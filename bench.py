@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Headline benchmark: fp16 -> fp32 GEMM TFLOP/s on B200, C = A . B^T, 8192^3 per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one launch of the sm_100a GEMM on one rank's operands.  With N GPUs
+(one process per GPU, launched by torch.distributed.run) the problem is the
+M-sharded configuration M = 8192*N, N = K = 8192: every rank owns an 8192-row
+slab of A and C and a replica of B, nothing is exchanged while the clock runs
+(weak scaling; at N = 8 this is the M = 65536 configuration).  Rank 0 prints ONE
+JSON line.  `--impl reference` times the CPU restatement of the reference's CPU
+GEMM (docs/nyc25.py:13-56) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fp16->fp32 GEMM TFLOP/s (8192^3 per GPU, M-sharded across GPUs)"
+UNIT = "TFLOP/s"
+M_PER_RANK = 8192
+N_DIM = 8192
+K_DIM = 8192
+FLOPS_PER_STEP = 2.0 * M_PER_RANK * N_DIM * K_DIM
+# algorithmic bytes of one launch: A + B read once, C written once
+BYTES_PER_STEP = 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM + 4 * M_PER_RANK * N_DIM
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel at this size (see profiles/)
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": float(p["bf16_tflops"]), "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", 0)),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def config_dict(world):
+    return {"workload": f"M-sharded fp16 GEMM: M={M_PER_RANK * world} N={N_DIM} K={K_DIM}, "
+                        f"{M_PER_RANK} rows of A and C per GPU, B replicated",
+            "layout": "A MxK row-major fp16, B NxK row-major fp16, C MxN row-major fp32, fp32 accumulation",
+            "values": "uniform [-1,1) from a position hash, seeds 20010106 / 19980724",
+            "parallelism": f"m-shard x{world}, no collective in the timed region",
+            "l2": "inputs exceed L2: A+B+C = 512 MiB per GPU against 126 MB of L2"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+               0x10: "sync_boost"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_sample(oracle, rows, a_rows=None, b=None):
+    """Time the CPU oracle GEMM on `rows` rows of A against the full B; returns (TFLOP/s, seconds)."""
+    if b is None:
+        b = oracle.fill_f16(N_DIM, K_DIM, oracle.DATA_UNIFORM_PM1, oracle.SEED_B)
+    if a_rows is None or a_rows.shape[0] != rows:
+        a_rows = oracle.fill_f16(rows, K_DIM, oracle.DATA_UNIFORM_PM1, oracle.SEED_A)
+    t0 = time.perf_counter()
+    oracle.gemm_f16f32(a_rows, b)
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * N_DIM * K_DIM / dt / 1e12, dt, a_rows, b
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's CPU GEMM (restated in oracle/) on this box's host cores."""
+    if rank != 0:
+        return
+    from oracle import oracle
+
+    threads = oracle.num_threads()
+    # size a step so that the whole run takes a couple of minutes at most
+    tf, dt, a_rows, b = cpu_sample(oracle, 64)
+    step_target_s = min(2.0, 60.0 / (args.steps + args.warmup))  # the whole run stays near a minute
+    rows = int(max(64, min(M_PER_RANK, (step_target_s / max(dt, 1e-6)) * 64)))
+    rows -= rows % 64
+    a_rows = None
+    for _ in range(args.warmup):
+        tf, dt, a_rows, b = cpu_sample(oracle, rows, a_rows, b)
+    times = []
+    for _ in range(args.steps):
+        tf, dt, a_rows, b = cpu_sample(oracle, rows, a_rows, b)
+        times.append(dt)
+    step_s = sum(times) / len(times)
+    value = 2.0 * rows * N_DIM * K_DIM / step_s / 1e12
+    sample = f"{rows} of {M_PER_RANK} rows of A against the full B ({2.0 * rows * N_DIM * K_DIM / 1e9:.0f} GFLOP per step)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic",
+            "config": config_dict(args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (N=1 runs it by default)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="profiling runs: only the warm-up and timed launches (no end-to-end, library or CPU legs)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+
+    import spork_b200 as sp
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- operands: this rank's slab of A, a replica of B (made on rank 0, broadcast over NVLink)
+    a = torch.empty((M_PER_RANK, K_DIM), dtype=torch.float16, device=dev)
+    b = torch.empty((N_DIM, K_DIM), dtype=torch.float16, device=dev)
+    c = torch.empty((M_PER_RANK, N_DIM), dtype=torch.float32, device=dev)
+    sp.init_test_data(a, sp.DATA_UNIFORM_PM1, sp.SEED_A, row0=rank * M_PER_RANK)
+    if rank == 0:
+        sp.init_test_data(b, sp.DATA_UNIFORM_PM1, sp.SEED_B, transpose_rule=True)
+    if dist is not None:
+        dist.broadcast(b, 0)
+    torch.cuda.synchronize()
+
+    def step():
+        sp.matmul_sm100(a, b, c)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sp.status()
+
+    # ---- timed region: K launches, one CUDA event pair per launch on the launching stream
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        events[0].record()
+        for i in range(args.steps):
+            step()
+            events[i + 1].record()
+        torch.cuda.synchronize()
+    barrier()
+    sp.status()
+    total_ms = events[0].elapsed_time(events[-1])
+    launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms_max = float(t.item())
+    ms_per_step = total_ms_max / args.steps
+    value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "ms_per_step": ms_per_step, "value": value, "unit": UNIT}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end through the host-buffer C-ABI entry: pinned host operands in, C back out, every step
+    e2e_steps = max(3, min(args.steps, 10))
+    ha = a.cpu().pin_memory()
+    hb = b.cpu().pin_memory()
+    hc = torch.empty((M_PER_RANK, N_DIM), dtype=torch.float32).pin_memory()
+    sp.matmul_sm100_htod(ha, hb, hc)  # allocates the staging buffers
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        sp.matmul_sm100_htod(ha, hb, hc)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = FLOPS_PER_STEP * world / float(t.item()) / 1e12
+    e2e_ok = bool(torch.equal(hc.to(dev), c))
+
+    # ---- context: the vendor library on the same operands, same protocol (not the product path)
+    cublas_tflops = None
+    if rank == 0:
+        try:
+            bt = b.t()
+            for _ in range(3):
+                torch.mm(a, bt)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(min(args.steps, 50)):
+                torch.mm(a, bt)
+            e1.record()
+            torch.cuda.synchronize()
+            cublas_tflops = FLOPS_PER_STEP / (e0.elapsed_time(e1) / min(args.steps, 50) * 1e-3) / 1e12
+        except Exception:
+            cublas_tflops = None
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    avg_launch_ms = sum(launch_ms) / len(launch_ms)
+    achieved = FLOPS_PER_STEP / (avg_launch_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                "peak_kind": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['bf16_tflops_sustained']})",
+                "frac_of_nominal_2250": achieved / 2250.0,
+                "kernel": "spork::gemm_sm100::gemm_kernel<2,256>", "algorithmic_bytes": BYTES_PER_STEP,
+                "avg_launch_ms": avg_launch_ms, "min_launch_ms": min(launch_ms)}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle
+
+        tf, dt, a_rows, b_host = cpu_sample(oracle, 64)
+        rows = int(max(64, min(M_PER_RANK, (12.0 / max(dt, 1e-6)) * 64)))  # about 12 s of CPU work
+        rows -= rows % 64
+        tf, dt, _, _ = cpu_sample(oracle, rows, None, b_host)
+        cpu_baseline = {"value": tf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                        "sample": f"{rows} of {M_PER_RANK} rows of A against the full B, {dt:.1f} s"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic", "config": config_dict(world),
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM,
+                    "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
+            "gpu_launches": args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "context": {"cublas_fp16_tflops_same_protocol": cublas_tflops, "frac_of_nominal_fp16_peak": value / (2250.0 * world)}}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

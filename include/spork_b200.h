@@ -84,6 +84,13 @@ int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void*
 int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
                              int transpose_rule, void* stream);
 
+/* Same fill for a window of a larger logical matrix: element (r, c) of the
+ * buffer takes the value of element (row0 + r, col0 + c).  A rank of an
+ * M-sharded run fills its own slab of A this way; the reference is single-GPU
+ * (gemm/gemm_main.cpp:10) and always fills whole matrices. */
+int spork_init_test_data_f16_at(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
+                                int transpose_rule, uint32_t row0, uint32_t col0, void* stream);
+
 /* The reference's oracle kernel restated for fp16 inputs: fp32 FFMA, k
  * ascending (gemm/gemm_baseline.cu:19-168).  Same operand layout as above. */
 int spork_gemm_baseline_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,

@@ -8,6 +8,13 @@ only).  There is no CPU fallback: every call raises if the library is missing
 or the device is not a B200-class GPU.
 """
 from .api import (  # noqa: F401
+    DATA_IDENTITY,
+    DATA_NORMAL,
+    DATA_RANDOM,
+    DATA_TILED_NUMBERS,
+    DATA_UNIFORM_PM1,
+    SEED_A,
+    SEED_B,
     SporkError,
     attn_fwd,
     compare_f32,

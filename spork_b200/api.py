@@ -16,6 +16,12 @@ import struct
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libspork_b200.so")
 
+# Fixture codes of init_test_data: 0..2 are the reference's TestDataCode (gemm/gemm_test.h:6-11).
+DATA_RANDOM, DATA_IDENTITY, DATA_TILED_NUMBERS, DATA_UNIFORM_PM1, DATA_NORMAL = range(5)
+# The reference's two hash constants (gemm/gemm_test.cu:73,86) seed the A and B operands.
+SEED_A = 20010106
+SEED_B = 19980724
+
 ERR_BASE = 10000
 _ERR_NAMES = {
     10001: "bad argument (null or misaligned pointer, unknown variant)",
@@ -63,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_htod_f16f32.restype = i32
         L.spork_init_test_data_f16.argtypes = [vp, u32, u32, i32, u32, i32, vp]
         L.spork_init_test_data_f16.restype = i32
+        L.spork_init_test_data_f16_at.argtypes = [vp, u32, u32, i32, u32, i32, u32, u32, vp]
+        L.spork_init_test_data_f16_at.restype = i32
         L.spork_gemm_baseline_f16f32.argtypes = [u32, u32, u32, vp, vp, vp, vp]
         L.spork_gemm_baseline_f16f32.restype = i32
         L.spork_compare_f32.argtypes = [vp, vp, u32, u32, vp, vp]
@@ -171,14 +179,17 @@ def matmul_sm100_htod(a_host, b_host, c_host=None):
     return c_host
 
 
-def init_test_data(t, code: int, seed: int = 0, transpose_rule: bool = False, stream=None):
-    """Fill the 2-D fp16 CUDA tensor ``t`` with fixture ``code`` (gemm/gemm_test.cu:55-96 plus codes 3, 4)."""
+def init_test_data(t, code: int, seed: int = 0, transpose_rule: bool = False, stream=None, row0: int = 0,
+                   col0: int = 0):
+    """Fill the 2-D fp16 CUDA tensor ``t`` with fixture ``code`` (gemm/gemm_test.cu:55-96 plus codes 3, 4).
+
+    ``row0``/``col0`` place ``t`` inside a larger logical matrix (a rank's slab of a sharded operand)."""
     import torch
 
     rows, cols = t.shape
     with torch.cuda.device(t.device):
-        rc = lib().spork_init_test_data_f16(_dev_ptr(t, torch.float16, "t"), rows, cols, code, seed & 0xFFFFFFFF,
-                                            int(transpose_rule), _stream_ptr(stream))
+        rc = lib().spork_init_test_data_f16_at(_dev_ptr(t, torch.float16, "t"), rows, cols, code, seed & 0xFFFFFFFF,
+                                               int(transpose_rule), row0, col0, _stream_ptr(stream))
     _check(rc, "spork_init_test_data_f16")
     return t
 

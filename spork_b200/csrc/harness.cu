@@ -70,14 +70,15 @@ __device__ inline __half fixture_value(uint32_t x, uint32_t y, int code, uint32_
 }
 
 __global__ void init_test_data_kernel(__half* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
-                                      bool transpose_rule)
+                                      bool transpose_rule, uint32_t row0, uint32_t col0)
 {
     const uint32_t tid_x = threadIdx.x + blockIdx.x * blockDim.x;
     const uint32_t tid_y = threadIdx.y + blockIdx.y * blockDim.y;
     for (uint32_t r = tid_y; r < rows; r += blockDim.y * gridDim.y) {
         for (uint32_t c = tid_x; c < cols; c += blockDim.x * gridDim.x) {
-            const uint32_t x = transpose_rule ? r : c;
-            const uint32_t y = transpose_rule ? c : r;
+            // (row0, col0): where this buffer sits inside the full logical matrix (a rank's slab)
+            const uint32_t x = transpose_rule ? r + row0 : c + col0;
+            const uint32_t y = transpose_rule ? c + col0 : r + row0;
             d_tensor[size_t(r) * cols + c] = fixture_value(x, y, code, seed);
         }
     }
@@ -183,6 +184,12 @@ __global__ void compare_kernel(const float* a_mat, const float* b_mat, uint32_t 
 extern "C" int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
                                         int transpose_rule, void* stream)
 {
+    return spork_init_test_data_f16_at(d_tensor, rows, cols, code, seed, transpose_rule, 0, 0, stream);
+}
+
+extern "C" int spork_init_test_data_f16_at(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
+                                           int transpose_rule, uint32_t row0, uint32_t col0, void* stream)
+{
     if (rows == 0 || cols == 0) {
         return 0;
     }
@@ -198,7 +205,7 @@ extern "C" int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t 
         grid.y = 4096;
     }
     spork::harness::init_test_data_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half*>(d_tensor), rows, cols, code, seed, transpose_rule != 0);
+        static_cast<__half*>(d_tensor), rows, cols, code, seed, transpose_rule != 0, row0, col0);
     return (int)cudaGetLastError();
 }
 

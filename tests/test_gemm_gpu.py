@@ -1,0 +1,300 @@
+"""Parity of the sm_100a GEMM with the CPU oracle, through the C ABI, on a B200.
+
+Follows the reference's own test method (gemm/gemm_test.cu): seeded position-hashed
+inputs, output poisoned with 0x7D bytes before each run, comparison of the whole
+result; plus the headline tolerance max|err| / (max|A| max|B| K 2^-10) <= 1.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1.0  # normalised error bound of the headline configurations (fp32 accumulation)
+
+
+def _inputs(sp, orc, cuda, M, N, K, code_a, code_b):
+    """Fixtures made on the device, read back so the oracle sees the exact bits the kernel reads."""
+    import torch
+
+    a = torch.empty((M, K), dtype=torch.float16, device=cuda)
+    b = torch.empty((N, K), dtype=torch.float16, device=cuda)
+    sp.init_test_data(a, code_a, orc.SEED_A)
+    # B is the logical K x N matrix stored transposed (the reference's d_bCol, gemm_test.cu:241)
+    sp.init_test_data(b, code_b, orc.SEED_B, transpose_rule=True)
+    return a, b
+
+
+def _poisoned(cuda, M, N):
+    import torch
+
+    c = torch.empty((M, N), dtype=torch.float32, device=cuda)
+    c.view(torch.uint8).fill_(0x7D)  # gemm_test.cu:244-247
+    return c
+
+
+def _check(sp, orc, a, b, c, K):
+    A, B, got = a.cpu().numpy(), b.cpu().numpy(), c.cpu().numpy()
+    ref = orc.gemm_f16f32(A, B)
+    amax = float(np.abs(A.astype(np.float32)).max()) if A.size else 0.0
+    bmax = float(np.abs(B.astype(np.float32)).max()) if B.size else 0.0
+    if amax == 0 or bmax == 0 or K == 0:
+        assert (got == 0).all()
+        return 0.0
+    err = orc.normalised_error(got, ref, amax, bmax, K)
+    assert err <= TOL, f"normalised error {err}"
+    return err
+
+
+def test_device_fixtures_match_the_oracle_bit_for_bit(sp, orc, cuda):
+    import torch
+
+    for code in range(5):
+        for transpose in (False, True):
+            t = torch.empty((70, 136), dtype=torch.float16, device=cuda)
+            sp.init_test_data(t, code, 101, transpose_rule=transpose)
+            want = orc.fill_f16(70, 136, code, 101, transpose)
+            assert (t.cpu().numpy().view(np.uint16) == want.view(np.uint16)).all(), (code, transpose)
+
+
+def test_baseline_kernel_is_bit_exact_with_the_oracle(sp, orc, cuda):
+    for M, N, K in ((256, 256, 512), (70, 130, 72)):
+        a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+        c = sp.gemm_baseline(a, b, _poisoned(cuda, M, N))
+        ref = orc.gemm_f16f32(a.cpu().numpy(), b.cpu().numpy())
+        assert (c.cpu().numpy() == ref).all()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+def test_config1_every_variant(sp, orc, cuda, cta_group, block_n):
+    """M=256 N=256 K=512, uniform [-1,1], the reference-sized CPU-checkable configuration."""
+    M, N, K = 256, 256, 512
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=cta_group)
+    sp.status()
+    err = _check(sp, orc, a, b, c, K)
+    assert err < 1e-3  # fp32 accumulation: far inside the bound
+
+
+@pytest.mark.parametrize("variant", [0, 64, 128, 256])
+def test_default_entry_point_variants(sp, orc, cuda, variant):
+    M, N, K = 384, 320, 264
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c, variant=variant)
+    sp.status()
+    _check(sp, orc, a, b, c, K)
+
+
+# Ragged and extreme shapes from the reference's list (gemm/gemm_main.cpp:98-122), scaled so the
+# CPU oracle finishes in seconds, plus shapes that straddle every tile edge.
+RAGGED = [(160, 480, 816), (768, 768, 32), (1, 8, 8), (129, 257, 72), (255, 4, 64), (1000, 264, 136),
+          (513, 1028, 200), (64, 2048, 1032), (2048, 64, 520), (300, 250, 64), (37, 53, 8), (128, 6, 4104)]
+
+
+@pytest.mark.parametrize("shape", RAGGED)
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_ragged_shapes(sp, orc, cuda, shape, cta_group):
+    M, N, K = shape
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    for block_n in (64, 256):
+        c = _poisoned(cuda, M, N)
+        sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=cta_group)
+        sp.status()
+        _check(sp, orc, a, b, c, K)
+
+
+@pytest.mark.parametrize("pair", ["tiled_x_identity", "identity_x_tiled", "random_x_random"])
+def test_reference_fixture_pairings_and_comparator(sp, orc, cuda, pair):
+    """The three data styles of gemm/gemm_main.cpp:81-95, judged by the reference's own comparator
+    (gemm/gemm_test.cu:131-154) on the device and on the host."""
+    M, N, K = 640, 384, 512
+    codes = {"tiled_x_identity": (orc.DATA_TILED_NUMBERS, orc.DATA_IDENTITY),
+             "identity_x_tiled": (orc.DATA_IDENTITY, orc.DATA_TILED_NUMBERS),
+             "random_x_random": (orc.DATA_RANDOM, orc.DATA_RANDOM)}[pair]
+    a, b = _inputs(sp, orc, cuda, M, N, K, *codes)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    base = sp.gemm_baseline(a, b, _poisoned(cuda, M, N))
+    first, max_diff = sp.compare_f32(base, c)
+    assert first is None, f"reference comparator failed first at {first}"
+    ref = orc.gemm_f16f32(a.cpu().numpy(), b.cpu().numpy())
+    assert orc.ratio_compare(ref, c.cpu().numpy()) is None
+    if pair != "random_x_random":
+        # exact small integers times one: the product must be exact, not merely close
+        assert (c.cpu().numpy() == ref).all()
+        assert max_diff == 0.0
+
+
+def test_comparator_localises_a_planted_error(sp, orc, cuda):
+    import torch
+
+    x = torch.ones((300, 200), dtype=torch.float32, device=cuda)
+    y = x.clone()
+    y[123, 45] = 1.2
+    y[200, 7] = -1.0
+    first, max_diff = sp.compare_f32(x, y)
+    assert first == (123, 45)
+    assert max_diff == pytest.approx(2.0)
+
+
+@pytest.mark.parametrize("split_k", [2, 3, 16, 1000])
+def test_split_k_reduce_add(sp, orc, cuda, split_k):
+    M, N, K = 384, 512, 2048
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    for cta_group in (1, 2):
+        c = _poisoned(cuda, M, N)
+        sp.matmul_sm100(a, b, c, block_n=128, cta_group=cta_group, split_k=split_k)
+        sp.status()
+        _check(sp, orc, a, b, c, K)
+
+
+def test_n_not_multiple_of_four_uses_guarded_stores(sp, orc, cuda):
+    for M, N, K in ((130, 67, 72), (256, 1, 64), (300, 131, 136)):
+        a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+        for split_k in (1, 2):
+            c = _poisoned(cuda, M, N)
+            sp.matmul_sm100(a, b, c, block_n=128, cta_group=2, split_k=split_k)
+            sp.status()
+            _check(sp, orc, a, b, c, K)
+
+
+def test_empty_and_degenerate_problems(sp, orc, cuda):
+    import torch
+
+    # K == 0: C is all zeros; M == 0 or N == 0: nothing to do
+    a = torch.empty((64, 0), dtype=torch.float16, device=cuda)
+    b = torch.empty((32, 0), dtype=torch.float16, device=cuda)
+    c = _poisoned(cuda, 64, 32)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    assert (c == 0).all()
+    a = torch.empty((0, 64), dtype=torch.float16, device=cuda)
+    b = torch.empty((32, 64), dtype=torch.float16, device=cuda)
+    sp.matmul_sm100(a, b, torch.empty((0, 32), dtype=torch.float32, device=cuda))
+    sp.status()
+    # all-zero operands
+    a = torch.zeros((128, 64), dtype=torch.float16, device=cuda)
+    b = torch.ones((128, 64), dtype=torch.float16, device=cuda)
+    c = _poisoned(cuda, 128, 128)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    assert (c == 0).all()
+
+
+def test_argument_errors_are_returned_not_trapped(sp, cuda):
+    import torch
+
+    L = sp.lib()
+    a = torch.zeros((128, 72), dtype=torch.float16, device=cuda)
+    b = torch.zeros((128, 72), dtype=torch.float16, device=cuda)
+    c = torch.zeros((128, 128), dtype=torch.float32, device=cuda)
+    assert L.spork_gemm_sm100_f16f32(128, 128, 12, a.data_ptr(), b.data_ptr(), c.data_ptr(), 0, None) == 10002
+    assert L.spork_gemm_sm100_f16f32(128, 128, 72, a.data_ptr() + 2, b.data_ptr(), c.data_ptr(), 0, None) == 10001
+    assert L.spork_gemm_sm100_f16f32(128, 128, 72, None, b.data_ptr(), c.data_ptr(), 0, None) == 10001
+    assert L.spork_gemm_sm100_f16f32(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 100, None) == 10001
+    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 3, 1, 0,
+                                        None) == 10001
+    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 2, 0, 0,
+                                        None) == 10001
+    with pytest.raises(TypeError):
+        sp.matmul_sm100(a.float(), b)
+    with pytest.raises(ValueError):
+        sp.matmul_sm100(a, b[:, :64].contiguous())
+    sp.status()  # nothing was launched, nothing timed out
+
+
+def test_host_buffer_entry_point(sp, orc, cuda):
+    import torch
+
+    M, N, K = 512, 384, 264
+    A = orc.fill_f16(M, K, orc.DATA_UNIFORM_PM1, orc.SEED_A)
+    B = orc.fill_f16(N, K, orc.DATA_UNIFORM_PM1, orc.SEED_B)
+    c = sp.matmul_sm100_htod(torch.from_numpy(A), torch.from_numpy(B))
+    ref = orc.gemm_f16f32(A, B)
+    assert orc.normalised_error(c.numpy(), ref, 1.0, 1.0, K) <= TOL
+    # a second, smaller call reuses the staging buffers
+    c2 = sp.matmul_sm100_htod(torch.from_numpy(A[:128].copy()), torch.from_numpy(B))
+    assert orc.normalised_error(c2.numpy(), ref[:128], 1.0, 1.0, K) <= TOL
+
+
+def test_non_default_stream_and_back_to_back_launches(sp, orc, cuda):
+    import torch
+
+    M, N, K = 512, 512, 1024
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    cs = [_poisoned(cuda, M, N) for _ in range(4)]
+    torch.cuda.synchronize()
+    for c in cs:
+        sp.matmul_sm100(a, b, c, stream=s)
+    sp.status(stream=s)
+    for c in cs[1:]:
+        assert torch.equal(c, cs[0])  # deterministic: same tiles, same order of accumulation
+    _check(sp, orc, a, b, cs[0], K)
+
+
+def test_headline_size_properties(sp, orc, cuda):
+    """8192^3 (the headline configuration): whole-matrix comparison against the CUDA-core comparison kernel,
+    CPU-oracle check of sampled row blocks including both matrix edges, and linearity in A."""
+    import torch
+
+    M = N = K = 8192
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    base = sp.gemm_baseline(a, b, _poisoned(cuda, M, N))
+    _, max_diff = sp.compare_f32(base, c)
+    assert max_diff / (K * 2.0 ** -10) <= TOL
+    assert max_diff / (K * 2.0 ** -10) < 1e-2
+    A, B = a.cpu().numpy(), b.cpu().numpy()
+    for m0 in (0, 4000, 8192 - 16):
+        ref = orc.gemm_f16f32_rows(A, B, m0, 16)
+        got = c[m0:m0 + 16].cpu().numpy()
+        assert orc.normalised_error(got, ref, 1.0, 1.0, K) < 1e-2
+    # linearity: (2A) B^T == 2 (A B^T) exactly (scaling by two is exact in fp16 and fp32)
+    c2 = _poisoned(cuda, M, N)
+    sp.matmul_sm100((a * 2).contiguous(), b, c2)
+    sp.status()
+    assert torch.equal(c2, c * 2)
+
+
+def test_reference_oracle_kernel_agrees_with_cpu_oracle(orc, cuda):
+    """Pins the CPU oracle: the reference's own matmul_baseline (gemm/gemm_baseline.cu, compiled unmodified
+    into oracle/_ref) must reproduce it bit for bit on fp16-representable inputs; its Ampere-generation TF32
+    kernel (gemm/gemm_sm80.cu) must agree within TF32 rounding."""
+    import os
+
+    import torch
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                        "libspork_ref.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/libspork_ref.so was not built (needs the reference tree at build time)")
+    L = ctypes.CDLL(path)
+    vp = ctypes.c_void_p
+    for f in (L.spork_ref_matmul_baseline, L.spork_ref_matmul_sm80):
+        f.argtypes = [ctypes.c_uint32] * 3 + [vp, vp, vp] + [ctypes.c_int] * 3 + [vp]
+    for M, N, K, code in ((256, 256, 512, orc.DATA_UNIFORM_PM1), (160, 480, 816, orc.DATA_UNIFORM_PM1),
+                          (768, 768, 1024, orc.DATA_RANDOM)):
+        A = orc.fill_f16(M, K, code, orc.SEED_A)
+        B = orc.fill_f16(N, K, code, orc.SEED_B)
+        ref = orc.gemm_f16f32(A, B)
+        a = torch.from_numpy(A.astype(np.float32)).to(cuda)
+        b = torch.from_numpy(B.astype(np.float32)).to(cuda)
+        c = torch.full((M, N), float("nan"), device=cuda)
+        assert L.spork_ref_matmul_baseline(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 0, 1, 0, None) == 0
+        torch.cuda.synchronize()
+        assert (c.cpu().numpy() == ref).all()
+        if L.spork_ref_matmul_sm80_supports(M, N, K):
+            c2 = torch.full((M, N), float("nan"), device=cuda)
+            assert L.spork_ref_matmul_sm80(M, N, K, a.data_ptr(), b.data_ptr(), c2.data_ptr(), 0, 1, 0, None) == 0
+            torch.cuda.synchronize()
+            # TF32 keeps 10 mantissa bits, as many as fp16: the inputs are exact, only summation order differs
+            assert orc.ratio_compare(ref, c2.cpu().numpy()) is None
