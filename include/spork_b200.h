@@ -65,6 +65,14 @@ int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, c
 int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                int block_n, int cta_group, int split_k, int max_ctas, void* stream);
 
+/* Process-wide tuning of later launches (benchmark sweeps; the defaults are the
+ * measured best).  stages: shared-memory ring depth, 0 = as deep as fits;
+ * group_m: m-tiles per raster group, 0 = default; l2_hints: bit 0 = A loads
+ * evict-last, bit 1 = B loads evict-last, bit 2 = B loads evict-first;
+ * backoff_ns: sleep between polls of the long waits, 0 = spin.  The reference
+ * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
+int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);
+
 /* Synchronises `stream`, then returns and clears the device status word of the
  * current device: 0, or SPORK_ERR_DEVICE_TIMEOUT if a kernel abandoned a
  * bounded wait (detail word through *detail when non-null).  Replaces the

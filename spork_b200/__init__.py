@@ -26,5 +26,6 @@ from .api import (  # noqa: F401
     matmul_sm100_htod,
     matmul_sm100_supports,
     status,
+    tune,
     version,
 )

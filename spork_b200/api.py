@@ -63,6 +63,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_f16f32.restype = i32
         L.spork_gemm_sm100_f16f32_ex.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, i32, i32, vp]
         L.spork_gemm_sm100_f16f32_ex.restype = i32
+        L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
+        L.spork_gemm_sm100_tune.restype = i32
         L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]
         L.spork_gemm_sm100_status.restype = i32
         L.spork_gemm_sm100_htod_f16f32.argtypes = [u32, u32, u32, vp, vp, vp]
@@ -150,6 +152,11 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
             rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cta_group or 2, split_k, max_ctas, sp)
     _check(rc, "spork_gemm_sm100_f16f32")
     return c
+
+
+def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0) -> None:
+    """Process-wide tuning knobs of later GEMM launches (see spork_gemm_sm100_tune in the header)."""
+    _check(lib().spork_gemm_sm100_tune(stages, group_m, l2_hints, backoff_ns), "spork_gemm_sm100_tune")
 
 
 def status(stream=None, device=None) -> None:

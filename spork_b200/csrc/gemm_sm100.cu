@@ -83,6 +83,10 @@ struct Params {
     uint32_t kb_per_split;       // K blocks per split
     uint32_t num_kb;             // ceil(K / kBlockK)
     uint32_t use_tma_store;      // 0: guarded scalar stores (N % 4 != 0)
+    uint32_t stages;             // ring depth in use (<= Config::kStages)
+    uint32_t group_m;            // raster: m-tiles per group
+    uint32_t l2_hints;           // bit 0: A loads evict_last, bit 1: B loads evict_last, bit 2: B loads evict_first
+    uint32_t backoff_ns;         // sleep between polls of the long (epilogue / producer) waits; 0 = spin
     float* C;
     uint32_t* status;            // device status word
 };
@@ -108,10 +112,10 @@ __device__ __forceinline__ WorkItem decode_item(const Params& p, uint32_t item)
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t split = item / tiles;
     const uint32_t t = item % tiles;
-    const uint32_t group_size = kGroupM * p.tiles_n;
+    const uint32_t group_size = p.group_m * p.tiles_n;
     const uint32_t g = t / group_size;
-    const uint32_t first_m = g * kGroupM;
-    const uint32_t gm = (p.tiles_m - first_m) < (uint32_t)kGroupM ? (p.tiles_m - first_m) : (uint32_t)kGroupM;
+    const uint32_t first_m = g * p.group_m;
+    const uint32_t gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
     const uint32_t r = t % group_size;
     w.m_tile = first_m + r % gm;
     w.n_tile = r / gm;
@@ -189,12 +193,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            const uint64_t pol_a = (p.l2_hints & 1u) ? l2_policy_evict_last() : l2_policy_evict_normal();
+            const uint64_t pol_b = (p.l2_hints & 2u) ? l2_policy_evict_last()
+                                   : (p.l2_hints & 4u) ? l2_policy_evict_first() : l2_policy_evict_normal();
             for (uint32_t item = group_id; item < num_items && ok; item += num_groups) {
                 const WorkItem w = decode_item(p, item);
                 const int32_t a_row = (int32_t)(w.m_tile * Cfg::kUmmaM + cta_rank * kBlockM);
                 const int32_t b_row = (int32_t)(w.n_tile * BLOCK_N + cta_rank * Cfg::kBRows);
                 for (uint32_t kb = w.kb_begin; kb < w.kb_end; ++kb) {
-                    if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag, p.backoff_ns)) {
                         report_timeout(p, abort_flag, 1, stage);
                         ok = false;
                         break;
@@ -204,18 +211,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t full = smem_u32(&bars->full[stage]);
                     if (CG == 1) {
                         mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-                        tma_load_2d(sa, &tmap_a, full, (int32_t)(kb * kBlockK), a_row);
-                        tma_load_2d(sb, &tmap_b, full, (int32_t)(kb * kBlockK), b_row);
+                        tma_load_2d_hint(sa, &tmap_a, full, (int32_t)(kb * kBlockK), a_row, pol_a);
+                        tma_load_2d_hint(sb, &tmap_b, full, (int32_t)(kb * kBlockK), b_row, pol_b);
                     } else {
                         // Both CTAs' bytes complete on the leader's barrier.
                         if (is_leader) {
                             mbar_arrive_expect_tx(full, Cfg::kStageBytes * 2);
                         }
                         const uint32_t leader_full = map_to_cta(full, 0);
-                        tma_load_2d_pair(sa, &tmap_a, leader_full, (int32_t)(kb * kBlockK), a_row);
-                        tma_load_2d_pair(sb, &tmap_b, leader_full, (int32_t)(kb * kBlockK), b_row);
+                        tma_load_2d_pair_hint(sa, &tmap_a, leader_full, (int32_t)(kb * kBlockK), a_row, pol_a);
+                        tma_load_2d_pair_hint(sb, &tmap_b, leader_full, (int32_t)(kb * kBlockK), b_row, pol_b);
                     }
-                    if (++stage == (uint32_t)Cfg::kStages) {
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -262,7 +269,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (CG == 2) {
                         umma_commit<CG>(map_to_cta(empty, 1));
                     }
-                    if (++stage == (uint32_t)Cfg::kStages) {
+                    if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -290,7 +297,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const WorkItem w = decode_item(p, item);
             const uint32_t buf = local & 1u;
             const uint32_t acc_phase = (local >> 1) & 1u;
-            if (!mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase, abort_flag)) {
+            if (!mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase, abort_flag, p.backoff_ns)) {
                 if (lane == 0) {
                     report_timeout(p, abort_flag, 3, 0x40 + buf);
                 }
@@ -423,6 +430,15 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
+// Process-wide tuning knobs (spork_gemm_sm100_tune); the defaults are the measured best.
+struct Tuning {
+    int stages = 0;       // 0 = as deep as shared memory allows
+    int group_m = 8;
+    int l2_hints = 0;
+    int backoff_ns = 0;
+};
+static Tuning g_tuning;
+
 template <int CG, int BLOCK_N>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
                   int max_ctas, DeviceState& dev, cudaStream_t stream)
@@ -455,6 +471,11 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     p.use_tma_store = (N % 4 == 0) ? 1u : 0u;
     p.C = C;
     p.status = dev.status_word;
+    const Tuning tune = g_tuning;
+    p.stages = (tune.stages >= 2 && tune.stages <= Cfg::kStages) ? (uint32_t)tune.stages : (uint32_t)Cfg::kStages;
+    p.group_m = tune.group_m >= 1 ? (uint32_t)tune.group_m : (uint32_t)kGroupM;
+    p.l2_hints = (uint32_t)tune.l2_hints;
+    p.backoff_ns = (uint32_t)tune.backoff_ns;
 
     CUtensorMap tmap_a, tmap_b, tmap_c;
     int rc = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, M, K, kBlockM, kBlockK);
@@ -557,6 +578,18 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
 
 }  // namespace gemm_sm100
 }  // namespace spork
+
+extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
+{
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 7 || backoff_ns < 0 || backoff_ns > 100000) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::gemm_sm100::g_tuning.stages = stages;
+    spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
+    spork::gemm_sm100::g_tuning.l2_hints = l2_hints;
+    spork::gemm_sm100::g_tuning.backoff_ns = backoff_ns;
+    return 0;
+}
 
 extern "C" int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K)
 {

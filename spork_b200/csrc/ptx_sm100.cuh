@@ -124,18 +124,27 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA
 // has given up, the others stop waiting at their next slow-path check.
 // Returns false if the wait was abandoned.
+// `backoff_ns` > 0 puts the thread to sleep between polls (for waits that are long
+// and not latency critical: fewer issued instructions, less power).
 template <bool kClusterScope = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t backoff_ns = 0)
 {
     for (uint32_t fast = 0; fast < 64; ++fast) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) {
             return true;
+        }
+        if (backoff_ns != 0u) {
+            __nanosleep(backoff_ns);
         }
     }
     const uint64_t deadline = global_timer_ns() + kWaitLimitNs;
     for (uint32_t spin = 0;; ++spin) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) {
             return true;
+        }
+        if (backoff_ns != 0u) {
+            __nanosleep(backoff_ns);
         }
         if ((spin & 63u) == 63u) {
             if (*abort_flag != 0u || global_timer_ns() > deadline) {
@@ -156,6 +165,50 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
 __device__ __forceinline__ void fence_proxy_async_smem()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// L2 eviction-priority policies for loads that carry a cache hint.
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ uint64_t l2_policy_evict_normal()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int32_t x,
+                                                 int32_t y, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t cluster_bar,
+                                                      int32_t x, int32_t y, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
 }
 
 // 2-D tile load, global -> this CTA's shared memory; completion bytes are
