@@ -65,6 +65,26 @@ int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, c
 int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                int block_n, int cta_group, int split_k, int max_ctas, void* stream);
 
+/* Allocation-free GEMM.  Has no counterpart in the reference (whose harness
+ * allocates freely, gemm/gemm_test.cu:218-226).  For callers that cannot
+ * allocate device memory at call time: code living inside an arena that already
+ * owns the GPU's memory, processes that lock their allocator after start-up,
+ * latency paths that cannot afford cudaMalloc's implicit synchronisation.
+ * Same product as spork_gemm_sm100_f16f32, computed as `split_k` (>= 1) partial
+ * products over ranges of K that are summed in a fixed order (bit-reproducible).
+ * All scratch (status word + split-K workspace) is a fixed 64 MiB array inside
+ * the library image, held by every GPU that loads the library until exit:
+ *   - split_k * M * ceil4(N) * 4 bytes must be <= 64 MiB, else SPORK_ERR_TOO_LARGE;
+ *   - the first call on a device resolves the array's device address and sets
+ *     kernel attributes: make it before any stream capture;
+ *   - calls on one device share the array: calls that may overlap on the GPU
+ *     race and must be serialised by the caller;
+ *   - M = N = K = 0 queries: synchronises `stream`, returns and clears
+ *     SPORK_ERR_DEVICE_TIMEOUT if a launch of this entry point gave up a wait.
+ * Calls no cudaMalloc / cudaFree / allocating library routine. */
+int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
+                                   int split_k, void* stream);
+
 /* Process-wide tuning of later launches (benchmark sweeps; the defaults are the
  * measured best).  stages: shared-memory ring depth, 0 = as deep as fits;
  * group_m: m-tiles per raster group, 0 = default; l2_hints: bit 0 = A loads

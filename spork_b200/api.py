@@ -63,6 +63,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_f16f32.restype = i32
         L.spork_gemm_sm100_f16f32_ex.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, i32, i32, vp]
         L.spork_gemm_sm100_f16f32_ex.restype = i32
+        L.spork_gemm_sm100_f16f32_static.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
+        L.spork_gemm_sm100_f16f32_static.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
         L.spork_gemm_sm100_tune.restype = i32
         L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]

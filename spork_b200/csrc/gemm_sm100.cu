@@ -101,7 +101,7 @@ struct Barriers {
 };
 
 struct WorkItem {
-    uint32_t m_tile, n_tile, kb_begin, kb_end;
+    uint32_t m_tile, n_tile, kb_begin, kb_end, split;
 };
 
 // Grouped raster (the superblock idea of gemm/gemm_sm90.cu:318-345): work items
@@ -119,6 +119,7 @@ __device__ __forceinline__ WorkItem decode_item(const Params& p, uint32_t item)
     const uint32_t r = t % group_size;
     w.m_tile = first_m + r % gm;
     w.n_tile = r / gm;
+    w.split = split;
     w.kb_begin = split * p.kb_per_split;
     const uint32_t e = w.kb_begin + p.kb_per_split;
     w.kb_end = e < p.num_kb ? e : p.num_kb;
@@ -133,7 +134,10 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
     atomicCAS(p.status, 0u, 0x80000000u | (role << 24) | ((where & 0xFFu) << 16) | (blockIdx.x & 0xFFFFu));
 }
 
-template <int CG, int BLOCK_N>
+// kWorkspace = true: each K split stores its partial tile into slab `split` of a
+// [split][M][N] fp32 workspace (tmap_c is then a 3-D map over it) instead of
+// writing or reduce-adding into C; a second kernel sums the slabs in a fixed order.
+template <int CG, int BLOCK_N, bool kWorkspace = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_c, const Params p)
@@ -318,7 +322,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (!rows_live || col >= p.N) {
                     continue;  // warp-uniform
                 }
-                if (p.use_tma_store) {
+                if (kWorkspace || p.use_tma_store) {
                     const uint32_t slab = slab0 + slab_sel * kSlabBytes;
                     slab_sel ^= 1u;
                     // The store issued two chunks ago read this slab; make sure it is done.
@@ -337,7 +341,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (p.split_k > 1) {
+                        if (kWorkspace) {
+                            tma_store_3d(&tmap_c, slab, (int32_t)col, (int32_t)row0, (int32_t)w.split);
+                        } else if (p.split_k > 1) {
                             tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
                         } else {
                             tma_store_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
@@ -576,8 +582,242 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     return SPORK_ERR_BAD_ARGUMENT;
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant: deterministic split-K through a workspace that lives
+// in a fixed device array of this module instead of allocated memory.
+//
+// Layout of the array: bytes [0, 256) hold the device status word of this
+// variant, bytes [256, 256 + kStaticWorkspaceBytes) the [split][M][ceil4(N)] fp32
+// partial products.  Every GPU that loads the library carries the array until
+// the process exits.
+
+constexpr size_t kStaticWorkspaceBytes = 64ull << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[256 + kStaticWorkspaceBytes];
+
+// C[m][n] = sum over slabs, in ascending slab order, of ws[slab][m][n] (row pitch `pitch` floats).
+__global__ void __launch_bounds__(256) reduce_slabs_kernel(const float* ws, float* C, uint32_t M, uint32_t N,
+                                                          uint32_t pitch, uint32_t slabs)
+{
+    const size_t total = (size_t)M * N;
+    const size_t slab_stride = (size_t)M * pitch;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t m = (uint32_t)(i / N), n = (uint32_t)(i % N);
+        const float* src = ws + (size_t)m * pitch + n;
+        float acc = src[0];
+        for (uint32_t s = 1; s < slabs; ++s) {
+            acc += src[s * slab_stride];
+        }
+        C[i] = acc;
+    }
+}
+
+struct StaticDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+static StaticDevice g_static_dev[kMaxDevices];
+static std::mutex g_static_mutex;
+
+template <int BLOCK_N>
+static int launch_static(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
+                         const StaticDevice& dev, int ordinal, cudaStream_t stream)
+{
+    constexpr int CG = 2;
+    using Cfg = Config<CG, BLOCK_N>;
+    auto kernel = gemm_kernel<CG, BLOCK_N, true>;
+    static std::once_flag attr_once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    std::call_once(attr_once[ordinal], [&] {
+        attr_err[ordinal] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    });
+    if (attr_err[ordinal] != cudaSuccess) {
+        return (int)attr_err[ordinal];
+    }
+    Params p{};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.tiles_m = (M + Cfg::kUmmaM - 1) / Cfg::kUmmaM;
+    p.tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
+    p.num_kb = (K + kBlockK - 1) / kBlockK;
+    if (split_k > p.num_kb) {
+        split_k = p.num_kb;
+    }
+    p.kb_per_split = (p.num_kb + split_k - 1) / split_k;
+    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.use_tma_store = 1;
+    p.C = C;
+    p.status = reinterpret_cast<uint32_t*>(dev.scratch);
+    p.stages = (uint32_t)Cfg::kStages;
+    p.group_m = (uint32_t)kGroupM;
+    p.l2_hints = 0;
+    p.backoff_ns = 0;
+
+    const uint32_t pitch = (N + 3u) & ~3u;  // rows of the workspace are multiples of 16 bytes
+    if ((size_t)p.split_k * M * pitch * sizeof(float) > kStaticWorkspaceBytes) {
+        return SPORK_ERR_TOO_LARGE;
+    }
+    float* ws = reinterpret_cast<float*>(dev.scratch + 256);
+
+    CUtensorMap tmap_a, tmap_b, tmap_ws;
+    int rc = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, M, K, kBlockM, kBlockK);
+    if (rc) {
+        return rc;
+    }
+    rc = make_tmap_2d(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, N, K, Cfg::kBRows, kBlockK);
+    if (rc) {
+        return rc;
+    }
+    {
+        EncodeTiledFn fn = encode_tiled_fn();
+        if (!fn) {
+            return SPORK_ERR_DRIVER;
+        }
+        const cuuint64_t dims[3] = {N, M, p.split_k};
+        const cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, (cuuint64_t)M * pitch * 4};
+        const cuuint32_t box[3] = {kEpiCols, 32, 1};
+        const cuuint32_t elem_strides[3] = {1, 1, 1};
+        if (fn(&tmap_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ws, dims, strides, box, elem_strides,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return SPORK_ERR_DRIVER;
+        }
+    }
+    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k;
+    uint32_t groups = (uint32_t)(dev.sm_count / CG);
+    if (groups == 0) {
+        groups = 1;
+    }
+    if (items < groups) {
+        groups = (uint32_t)items;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(groups * CG, 1, 1);
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, tmap_ws, p);
+    if (e != cudaSuccess) {
+        return (int)e;
+    }
+    const size_t total = (size_t)M * N;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)dev.sm_count * 8 ? (total + 255) / 256
+                                                                                         : (size_t)dev.sm_count * 8);
+    reduce_slabs_kernel<<<blocks, 256, 0, stream>>>(ws, C, M, N, pitch, p.split_k);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace gemm_sm100
 }  // namespace spork
+
+// For callers that must not allocate device memory when they call into this
+// library - code running inside a memory arena that already owns the whole GPU,
+// a process whose device allocator is locked down after start-up, a latency
+// path where cudaMalloc's implicit synchronisation is not acceptable.  The
+// other GEMM entry points allocate a status word on a device's first call;
+// this one touches only a fixed array that is part of the library image.
+//
+// Computes the same product as spork_gemm_sm100_f16f32 with K cut into
+// `split_k` ranges (>= 1) whose partial products are summed in a fixed order,
+// so the result is bit-reproducible for a given split_k.
+//
+// Limits and rules:
+//   * split_k * M * ceil4(N) * 4 bytes must fit the 64 MiB workspace, otherwise
+//     SPORK_ERR_TOO_LARGE is returned and nothing is launched;
+//   * the first call on each device looks up the array's device address
+//     (with that device current) and sets the kernel's shared-memory limit;
+//     make that first call before any stream capture starts;
+//   * all calls on a device share the one workspace and status word: two calls
+//     whose kernels may overlap on the GPU (different streams) race - serialise
+//     them; the workspace keeps the last call's partial sums, nothing in it
+//     needs to start at zero, the status word is cleared at set-up;
+//   * M = N = K = 0 is a query: it synchronises `stream` and returns
+//     SPORK_ERR_DEVICE_TIMEOUT (clearing the word) if a kernel launched through
+//     this entry point abandoned a bounded wait, else 0.
+// It calls no cudaMalloc, cudaFree, or any allocating library routine.
+extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B,
+                                              float* C, int split_k, void* stream_)
+{
+    using namespace spork::gemm_sm100;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int ordinal = 0;
+    cudaError_t e = cudaGetDevice(&ordinal);
+    if (e != cudaSuccess) {
+        return (int)e;
+    }
+    if (ordinal < 0 || ordinal >= spork::kMaxDevices) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    StaticDevice dev;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        StaticDevice& d = g_static_dev[ordinal];
+        if (!d.ready) {
+            int major = 0, sms = 0;
+            if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, ordinal)) != cudaSuccess ||
+                (e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ordinal)) != cudaSuccess) {
+                return (int)e;
+            }
+            if (major != 10) {
+                return SPORK_ERR_NO_SM100;
+            }
+            // In host code `g_static_scratch` is only a handle for the symbol, not a device
+            // address: ask the runtime for the address on the current device.
+            void* ptr = nullptr;
+            if ((e = cudaGetSymbolAddress(&ptr, g_static_scratch)) != cudaSuccess) {
+                return (int)e;
+            }
+            if ((e = cudaMemset(ptr, 0, 256)) != cudaSuccess) {
+                return (int)e;
+            }
+            d.scratch = static_cast<unsigned char*>(ptr);
+            d.sm_count = sms;
+            d.ready = true;
+        }
+        dev = d;
+    }
+    if (M == 0 && N == 0 && K == 0) {  // status query
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) {
+            return (int)e;
+        }
+        uint32_t word = 0;
+        if ((e = cudaMemcpy(&word, dev.scratch, sizeof(word), cudaMemcpyDeviceToHost)) != cudaSuccess) {
+            return (int)e;
+        }
+        if (word != 0) {
+            cudaMemset(dev.scratch, 0, sizeof(word));
+            return SPORK_ERR_DEVICE_TIMEOUT;
+        }
+        return 0;
+    }
+    if (!spork_gemm_sm100_supports(M, N, K)) {
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    if (M == 0 || N == 0) {
+        return 0;
+    }
+    if (split_k < 1 || !C || !aligned16(C) || (K != 0 && (!A || !B || !aligned16(A) || !aligned16(B)))) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    if (K == 0) {
+        return (int)cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N, stream);
+    }
+    if (N <= 64) {
+        return launch_static<64>(M, N, K, A, B, C, (uint32_t)split_k, dev, ordinal, stream);
+    }
+    if (N <= 128) {
+        return launch_static<128>(M, N, K, A, B, C, (uint32_t)split_k, dev, ordinal, stream);
+    }
+    return launch_static<256>(M, N, K, A, B, C, (uint32_t)split_k, dev, ordinal, stream);
+}
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
