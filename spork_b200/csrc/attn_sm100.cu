@@ -1,0 +1,627 @@
+// Attention forward for sm_100a (B200): O = softmax(Q K^T * scale) V per head,
+// fp16 in, fp32 softmax, fp16 out, non-causal.
+//
+// Takes the place of the reference's attention launch entry
+// (launch_tk_4090_fwd_kernel / htod_f32_tk_4090_fwd, tk_4090_fwd.hpp:5-7; the
+// kernel source itself is not part of the reference tree) and computes the
+// math of simple_attn (torch_attn.py:11-16).
+//
+// One CTA owns TWO 128-row query tiles of one head and streams the head's keys
+// and values through them in blocks of 128, FlashAttention style:
+//   warps 0-3  softmax of query tile 0 (one thread = one query row)
+//   warps 4-7  softmax of query tile 1
+//   warp  8    TMA producer (Q tiles once, then K_j, V_j through a ring)
+//   warp  9    tcgen05.mma issuer (one thread) and TMEM owner
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
+// Per key block j and query tile w:
+//   S_w = Q_w K_j^T            tcgen05.mma, both operands K-major in shared memory
+//   softmax thread: row max, p = exp2((s - m) * scale*log2e), row sum; P_w (fp16)
+//       is written to shared memory in the 128B-swizzled K-major operand layout;
+//       when the running max moved, O_w is rescaled in place (tcgen05.ld/st)
+//   O_w += P_w V_j             tcgen05.mma, A = P_w (K-major), B = V_j (N-major)
+// The two query tiles alternate, so the tensor core works on one tile while the
+// other tile's softmax runs.  Keys past the end of a ragged sequence are masked
+// to -inf; rows past the end are computed on zero-filled queries and not stored.
+// Every wait is bounded (see ptx_sm100.cuh).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <math.h>
+#include <mutex>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/spork_b200.h"
+#include "device_state.h"
+#include "ptx_sm100.cuh"
+
+namespace spork {
+namespace attn_sm100 {
+
+using namespace ptx;
+
+constexpr int kTileQ = 128;     // query rows per tile (= TMEM lanes)
+constexpr int kTileKV = 128;    // keys per block
+constexpr int kNumThreads = 320;
+constexpr int kLoadWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kKvStages = 3;
+constexpr int kTmemCols = 512;
+
+template <int D>
+struct Config {
+    static_assert(D == 64 || D == 128, "head dimension");
+    static constexpr int kAtoms = D / 64;                      // 64-wide (128-byte) column blocks of a tile
+    static constexpr int kTileBytes = kTileQ * D * 2;          // a Q, K or V tile
+    static constexpr int kAtomBytes = 128 * 128;               // 128 rows x 128 bytes
+    static constexpr int kPBytes = kTileQ * kTileKV * 2;       // one P tile (fp16): 2 atoms
+    static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + kKvStages * kTileBytes + 2 * kPBytes + 1024;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+struct Params {
+    int BH, S, D;
+    int q_pairs;        // ceil(S / 256): CTAs per head
+    int kv_blocks;      // ceil(S / 128)
+    float scale_log2e;  // scale * log2(e)
+    __half* o;
+    uint32_t* status;
+};
+
+struct Barriers {
+    uint64_t q_full;
+    uint64_t kv_full[kKvStages];
+    uint64_t kv_empty[kKvStages];
+    uint64_t s_full[2];
+    uint64_t p_ready[2];
+    uint64_t pv_done[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+{
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_t* abort_flag, uint32_t role,
+                                               uint32_t where)
+{
+    *abort_flag = 1u;
+    atomicCAS(p.status, 0u, 0x90000000u | (role << 24) | ((where & 0xFFu) << 16) | (blockIdx.x & 0xFFFFu));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kNumThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const Params p)
+{
+    using Cfg = Config<D>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t warp = threadIdx.x / 32;
+    const uint32_t lane = threadIdx.x % 32;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;                                  // 2 Q tiles
+    const uint32_t kv_smem = q_smem + 2 * Cfg::kTileBytes;              // ring of K / V tiles
+    const uint32_t p_smem = kv_smem + kKvStages * Cfg::kTileBytes;      // 2 P tiles
+    Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (p_smem + 2 * Cfg::kPBytes - smem_u32(smem_raw)));
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    const int head = blockIdx.x / p.q_pairs;
+    const int q_pair = blockIdx.x % p.q_pairs;
+    const int q_row0 = q_pair * 2 * kTileQ;
+    const int n_blocks = p.kv_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(smem_u32(&bars->kv_full[s]), 1);
+            mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+        }
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(smem_u32(&bars->s_full[w]), 1);
+            mbar_init(smem_u32(&bars->p_ready[w]), kTileQ);
+            mbar_init(smem_u32(&bars->pv_done[w]), 1);
+        }
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc<1>(smem_u32(&bars->tmem_base), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    // column offsets inside the allocation
+    const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128
+    const uint32_t tmem_o0 = tmem_base + 256;    // O_w at + w * 128
+
+    if (warp == kLoadWarp) {
+        // ---------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            const uint32_t qf = smem_u32(&bars->q_full);
+            mbar_arrive_expect_tx(qf, 2 * Cfg::kTileBytes);
+            for (int w = 0; w < 2; ++w) {
+                for (int a = 0; a < Cfg::kAtoms; ++a) {
+                    tma_load_3d(q_smem + w * Cfg::kTileBytes + a * Cfg::kAtomBytes, &tmap_q, qf, a * 64,
+                                q_row0 + w * kTileQ, head);
+                }
+            }
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = 0; t < 2 * n_blocks && ok; ++t) {
+                // tile order: K_0, V_0, K_1, V_1, ...
+                const int j = t >> 1;
+                const CUtensorMap* map = (t & 1) ? &tmap_v : &tmap_k;
+                if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, abort_flag)) {
+                    report_timeout(p, abort_flag, 1, stage);
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = smem_u32(&bars->kv_full[stage]);
+                mbar_arrive_expect_tx(full, Cfg::kTileBytes);
+                for (int a = 0; a < Cfg::kAtoms; ++a) {
+                    tma_load_3d(kv_smem + stage * Cfg::kTileBytes + a * Cfg::kAtomBytes, map, full, a * 64,
+                                j * kTileKV, head);
+                }
+                if (++stage == (uint32_t)kKvStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false);
+            constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true);  // B = V is N-major
+            uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
+            bool ok = true;
+            auto advance = [&]() {
+                if (++stage == (uint32_t)kKvStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            };
+            // S_w = Q_w K^T from the K tile in ring slot `st`
+            auto issue_qk = [&](int w, uint32_t st) {
+                const uint32_t qa = q_smem + w * Cfg::kTileBytes;
+                const uint32_t kb = kv_smem + st * Cfg::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t da = umma_desc_kmajor_sw128(qa + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
+                    const uint64_t db = umma_desc_kmajor_sw128(kb + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
+                    umma_f16_ss<1>(tmem_s0 + w * 128, da, db, idesc_qk, kk != 0 ? 1u : 0u);
+                }
+            };
+            // O_w (+)= P_w V from the V tile in ring slot `st`
+            auto issue_pv = [&](int w, uint32_t st, bool accumulate) {
+                const uint32_t pa = p_smem + w * Cfg::kPBytes;
+                const uint32_t vb = kv_smem + st * Cfg::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < kTileKV / 16; ++kk) {
+                    const uint64_t da = umma_desc_kmajor_sw128(pa + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
+                    // 16 keys = 16 rows of 128 bytes further down the V tile; d-halves are one atom apart
+                    const uint64_t db = umma_desc_mnmajor_sw128(vb + kk * 16 * 128, Cfg::kAtomBytes, 1024);
+                    umma_f16_ss<1>(tmem_o0 + w * 128, da, db, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
+                }
+            };
+            do {
+                if (!mbar_wait(smem_u32(&bars->q_full), 0, abort_flag)) {
+                    report_timeout(p, abort_flag, 2, 0x20);
+                    break;
+                }
+                // prologue: S_0(0), S_1(0)
+                if (!mbar_wait(smem_u32(&bars->kv_full[stage]), phase, abort_flag)) {
+                    report_timeout(p, abort_flag, 2, stage);
+                    break;
+                }
+                tcgen05_fence_after();
+                for (int w = 0; w < 2; ++w) {
+                    issue_qk(w, stage);
+                    umma_commit<1>(smem_u32(&bars->s_full[w]));
+                }
+                umma_commit<1>(smem_u32(&bars->kv_empty[stage]));
+                advance();
+                for (int j = 0; j < n_blocks && ok; ++j) {
+                    const uint32_t v_stage = stage, v_phase = phase;
+                    advance();
+                    const uint32_t k_stage = stage, k_phase = phase;  // K_{j+1}, if any
+                    const bool more = j + 1 < n_blocks;
+                    if (more) {
+                        advance();
+                    }
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        if (!mbar_wait(smem_u32(&bars->p_ready[w]), (uint32_t)(j & 1), abort_flag)) {
+                            report_timeout(p, abort_flag, 2, 0x30 + w);
+                            ok = false;
+                            break;
+                        }
+                        if (w == 0 && !mbar_wait(smem_u32(&bars->kv_full[v_stage]), v_phase, abort_flag)) {
+                            report_timeout(p, abort_flag, 2, v_stage);
+                            ok = false;
+                            break;
+                        }
+                        tcgen05_fence_after();
+                        issue_pv(w, v_stage, j > 0);
+                        umma_commit<1>(smem_u32(&bars->pv_done[w]));
+                        if (w == 1) {
+                            umma_commit<1>(smem_u32(&bars->kv_empty[v_stage]));
+                        }
+                        if (more) {
+                            if (w == 0 && !mbar_wait(smem_u32(&bars->kv_full[k_stage]), k_phase, abort_flag)) {
+                                report_timeout(p, abort_flag, 2, k_stage);
+                                ok = false;
+                                break;
+                            }
+                            tcgen05_fence_after();
+                            issue_qk(w, k_stage);
+                            umma_commit<1>(smem_u32(&bars->s_full[w]));
+                            if (w == 1) {
+                                umma_commit<1>(smem_u32(&bars->kv_empty[k_stage]));
+                            }
+                        }
+                    }
+                }
+            } while (false);
+        }
+    } else {
+        // --------------------------------------------------------------- softmax
+        const uint32_t w = warp / 4;        // query tile of this warpgroup
+        const uint32_t quarter = warp % 4;  // TMEM lanes [32*quarter, +32)
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32u) << 16;
+        const uint32_t tmem_s = tmem_s0 + w * 128 + lane_addr;
+        const uint32_t tmem_o = tmem_o0 + w * 128 + lane_addr;
+        // this row inside a P atom: 8-row groups of 1024 bytes, 16-byte chunks XORed with (row & 7)
+        const uint32_t p_row = p_smem + w * Cfg::kPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+        const float sl2 = p.scale_log2e;
+        float m_run = -INFINITY;  // running row max (raw scores)
+        float l_run = 0.0f;       // running row sum
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, 20)) {
+                if (lane == 0) {
+                    report_timeout(p, abort_flag, 3, 0x10 + w);
+                }
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const int valid = p.S - j * kTileKV;  // keys of this block that exist
+            const bool ragged = valid < kTileKV;  // uniform over the CTA
+            // pass 1: row max
+            float m_blk = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < kTileKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_s + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(r[i]);
+                    if (ragged && c * 32 + i >= valid) {
+                        s = -INFINITY;
+                    }
+                    m_blk = fmaxf(m_blk, s);
+                }
+            }
+            const float m_new = fmaxf(m_run, m_blk);
+            const float alpha = ex2_approx((m_run - m_new) * sl2);  // 0 on the first block (m_run = -inf)
+            const float neg_m = -m_new * sl2;
+            // The previous P_w V MMA must be done before P_w is overwritten and O_w touched.
+            if (j > 0) {
+                if (!mbar_wait(smem_u32(&bars->pv_done[w]), (uint32_t)((j - 1) & 1), abort_flag)) {
+                    if (lane == 0) {
+                        report_timeout(p, abort_flag, 3, 0x20 + w);
+                    }
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+            }
+            // pass 2: p = exp2(s * sl2 - m * sl2), row sum, P (fp16) to shared memory
+            float l_blk = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kTileKV / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_s + c * 32, r);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s0 = __uint_as_float(r[2 * i]);
+                    float s1 = __uint_as_float(r[2 * i + 1]);
+                    if (ragged) {
+                        if (c * 32 + 2 * i >= valid) {
+                            s0 = -INFINITY;
+                        }
+                        if (c * 32 + 2 * i + 1 >= valid) {
+                            s1 = -INFINITY;
+                        }
+                    }
+                    const float p0 = ex2_approx(fmaf(s0, sl2, neg_m));
+                    const float p1 = ex2_approx(fmaf(s1, sl2, neg_m));
+                    l_blk += p0 + p1;
+                    packed[i] = pack_half2(p0, p1);
+                }
+                // columns [32c, 32c+32) = atom c/2, 16-byte chunks (c%2)*4 .. +3
+                const uint32_t atom_addr = p_row + (c >> 1) * Cfg::kAtomBytes;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint32_t chunk = (uint32_t)((c & 1) * 4 + q4);
+                    st_shared_v4(atom_addr + ((chunk ^ (row & 7u)) << 4), packed[4 * q4], packed[4 * q4 + 1],
+                                 packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+            l_run = l_run * alpha + l_blk;
+            m_run = m_new;
+            // rescale O_w when some row of this warp moved its max (never on the first block: O is not yet written)
+            if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+#pragma unroll 1
+                for (int c = 0; c < D / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(tmem_o + c * 16, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    }
+                    tmem_st_32x32b_x16(tmem_o + c * 16, r);
+                }
+                tmem_st_wait();
+            }
+            fence_proxy_async_smem();  // P stores -> visible to the MMA's shared-memory reads
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&bars->p_ready[w]));
+        }
+        // ---- epilogue: O_w / l -> fp16 -> global
+        if (ok) {
+            if (!mbar_wait(smem_u32(&bars->pv_done[w]), (uint32_t)((n_blocks - 1) & 1), abort_flag)) {
+                if (lane == 0) {
+                    report_timeout(p, abort_flag, 3, 0x28 + w);
+                }
+                ok = false;
+            }
+        }
+        if (ok) {
+            tcgen05_fence_after();
+            const float inv_l = 1.0f / l_run;
+            const int q_row = q_row0 + (int)w * kTileQ + (int)row;
+            __half* dst = p.o + ((size_t)head * p.S + (size_t)(q_row < p.S ? q_row : 0)) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_o + c * 32, r);
+                tmem_ld_wait();
+                if (q_row < p.S) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_half2(__uint_as_float(r[8 * q4 + 0]) * inv_l, __uint_as_float(r[8 * q4 + 1]) * inv_l);
+                        v.y = pack_half2(__uint_as_float(r[8 * q4 + 2]) * inv_l, __uint_as_float(r[8 * q4 + 3]) * inv_l);
+                        v.z = pack_half2(__uint_as_float(r[8 * q4 + 4]) * inv_l, __uint_as_float(r[8 * q4 + 5]) * inv_l);
+                        v.w = pack_half2(__uint_as_float(r[8 * q4 + 6]) * inv_l, __uint_as_float(r[8 * q4 + 7]) * inv_l);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    // ----------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+// [BH][S][D] fp16 tensor, boxes of 128 rows x 64 columns (128 bytes, swizzled) of one head.
+static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int D)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        return SPORK_ERR_DRIVER;
+    }
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)BH};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                          elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
+}
+
+template <int D>
+static int launch(int BH, int S, const void* q, const void* k, const void* v, void* o, float scale, DeviceState& dev,
+                  cudaStream_t stream)
+{
+    using Cfg = Config<D>;
+    auto kernel = attn_fwd_kernel<D>;
+    static std::once_flag attr_once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    std::call_once(attr_once[dev.ordinal], [&] {
+        attr_err[dev.ordinal] =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    });
+    if (attr_err[dev.ordinal] != cudaSuccess) {
+        return (int)attr_err[dev.ordinal];
+    }
+    Params p{};
+    p.BH = BH;
+    p.S = S;
+    p.D = D;
+    p.q_pairs = (S + 2 * kTileQ - 1) / (2 * kTileQ);
+    p.kv_blocks = (S + kTileKV - 1) / kTileKV;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.o = static_cast<__half*>(o);
+    p.status = dev.status_word;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tmap_bsd(&tq, q, BH, S, D)) != 0 || (rc = make_tmap_bsd(&tk, k, BH, S, D)) != 0 ||
+        (rc = make_tmap_bsd(&tv, v, BH, S, D)) != 0) {
+        return rc;
+    }
+    const long long ctas = (long long)BH * p.q_pairs;
+    if (ctas > 0x7FFFFFFFll) {
+        return SPORK_ERR_TOO_LARGE;
+    }
+    kernel<<<(unsigned)ctas, kNumThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
+    return (int)cudaGetLastError();
+}
+
+__global__ void f32_to_f16_kernel(const float* src, __half* dst, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        dst[i] = __float2half_rn(src[i]);
+    }
+}
+
+__global__ void f16_to_f32_kernel(const __half* src, float* dst, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        dst[i] = __half2float(src[i]);
+    }
+}
+
+}  // namespace attn_sm100
+}  // namespace spork
+
+extern "C" int spork_attn_sm100_supports(int BH, int S, int D)
+{
+    return (BH >= 0 && S >= 0 && (D == 64 || D == 128)) ? 1 : 0;
+}
+
+extern "C" int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,
+                                        float scale, void* stream)
+{
+    if (!spork_attn_sm100_supports(BH, S, D)) {
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    if (BH == 0 || S == 0) {
+        return 0;
+    }
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !(scale >= 0.0f)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::DeviceState* dev = nullptr;
+    const int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (D == 64) {
+        return spork::attn_sm100::launch<64>(BH, S, q, k, v, o, scale, *dev, s);
+    }
+    return spork::attn_sm100::launch<128>(BH, S, q, k, v, o, scale, *dev, s);
+}
+
+// Same signature and meaning as the reference's htod_f32_tk_4090_fwd
+// (tk_4090_fwd.hpp:7): host fp32 (N, d) matrices in, host fp32 out, one head,
+// scale 1/sqrt(d).  Inputs are rounded to fp16 on the device.  On failure the
+// output is filled with NaN and a message goes to stderr (the reference's
+// entry point returns void as well).
+extern "C" void htod_f32_attn_sm100_fwd(int N, int d, const float* q, const float* k, const float* v, float* o)
+{
+    using namespace spork::attn_sm100;
+    auto fail = [&](const char* what, int code) {
+        fprintf(stderr, "htod_f32_attn_sm100_fwd: %s (code %d)\n", what, code);
+        if (o && N > 0 && d > 0) {
+            for (size_t i = 0; i < (size_t)N * d; ++i) {
+                o[i] = NAN;
+            }
+        }
+    };
+    if (N <= 0 || d <= 0) {
+        return;
+    }
+    if (!q || !k || !v || !o || !spork_attn_sm100_supports(1, N, d)) {
+        fail("unsupported shape or null pointer (d must be 64 or 128)", SPORK_ERR_UNSUPPORTED_SHAPE);
+        return;
+    }
+    spork::DeviceState* dev = nullptr;
+    int rc = spork::current_device_state(&dev);
+    if (rc) {
+        fail("no usable device", rc);
+        return;
+    }
+    const size_t n = (size_t)N * d;
+    // slot 0: fp32 staging (n floats), slot 1: q,k,v,o fp16 (4n halves)
+    if ((rc = spork::ensure_staging(*dev, 0, n * sizeof(float))) != 0 ||
+        (rc = spork::ensure_staging(*dev, 1, 4 * n * sizeof(__half) + 64)) != 0) {
+        fail("staging allocation", rc);
+        return;
+    }
+    cudaStream_t s = cudaStreamPerThread;
+    float* f32 = static_cast<float*>(dev->staging[0]);
+    __half* h = static_cast<__half*>(dev->staging[1]);
+    const size_t n_pad = (n + 7) & ~size_t(7);  // keeps every fp16 matrix 16-byte aligned
+    const float* src[3] = {q, k, v};
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+        e = cudaMemcpyAsync(f32, src[i], n * sizeof(float), cudaMemcpyHostToDevice, s);
+        f32_to_f16_kernel<<<blocks, 256, 0, s>>>(f32, h + i * n_pad, n);
+    }
+    if (e != cudaSuccess) {
+        fail("copy to device", (int)e);
+        return;
+    }
+    rc = spork_attn_sm100_fwd_f16(1, N, d, h, h + n_pad, h + 2 * n_pad, h + 3 * n_pad, 1.0f / sqrtf((float)d), s);
+    if (rc) {
+        fail("launch", rc);
+        return;
+    }
+    f16_to_f32_kernel<<<blocks, 256, 0, s>>>(h + 3 * n_pad, f32, n);
+    e = cudaMemcpyAsync(o, f32, n * sizeof(float), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) {
+        fail("copy to host", (int)e);
+        return;
+    }
+    rc = spork_gemm_sm100_status(s, nullptr);
+    if (rc) {
+        fail("device status", rc);
+    }
+}

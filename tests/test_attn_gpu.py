@@ -1,0 +1,144 @@
+"""Parity of the sm_100a attention forward with the CPU oracle (the math of the reference's simple_attn,
+torch_attn.py:11-16), through the C ABI, on a B200."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# fp16 probabilities (P is rounded to fp16 before P.V, relative step 2^-11) and fp16 output:
+# |o - o_ref| <= ATOL + RTOL * |o_ref| with o_ref the oracle's fp32 result.
+ATOL = 2e-3
+RTOL = 1e-2
+
+
+def _close(got, ref):
+    got = got.astype(np.float32)
+    bad = np.abs(got - ref) > ATOL + RTOL * np.abs(ref)
+    return not bad.any(), float(np.abs(got - ref).max())
+
+
+def _qkv(sp, cuda, BH, S, D, seed=101):
+    import torch
+
+    ts = []
+    # seeds s, s^888, s^1776 as in matrix_util.hpp:53-55
+    for sd in (seed, seed ^ 888, seed ^ 1776):
+        t = torch.empty((BH * S, D), dtype=torch.float16, device=cuda)
+        sp.init_test_data(t, sp.DATA_NORMAL, sd)
+        ts.append(t.view(BH, S, D))
+    return ts
+
+
+@pytest.mark.parametrize("BH,S,D", [(1, 256, 64), (2, 256, 128), (3, 512, 128), (2, 1024, 64), (1, 128, 128),
+                                    (5, 384, 128)])
+def test_attention_matches_oracle(sp, orc, cuda, BH, S, D):
+    q, k, v = _qkv(sp, cuda, BH, S, D)
+    o = sp.attn_fwd(q, k, v)
+    sp.status()
+    _, ref = orc.attn_f16(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    ok, worst = _close(o.cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+
+
+@pytest.mark.parametrize("BH,S,D", [(2, 200, 128), (1, 1, 64), (3, 129, 64), (2, 257, 128), (1, 100, 128), (2, 2560, 64)])
+def test_ragged_sequence_lengths(sp, orc, cuda, BH, S, D):
+    """Sequence lengths that are not multiples of the 128-key block or the 256-row CTA (keys past the end are
+    masked, rows past the end are not stored); 2560 x 64 is the size of the reference's script (torch_attn.py:26)."""
+    import torch
+
+    q, k, v = _qkv(sp, cuda, BH, S, D, seed=237)
+    o = torch.full((BH, S, D), float("nan"), dtype=torch.float16, device=cuda)
+    guard = torch.full((64,), 7.0, dtype=torch.float16, device=cuda)  # must survive: nothing is written past o
+    sp.attn_fwd(q, k, v, o)
+    sp.status()
+    _, ref = orc.attn_f16(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    ok, worst = _close(o.cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+    assert (guard == 7.0).all()
+
+
+@pytest.mark.parametrize("name", ["n256_d64", "n320_d128"])
+def test_golden_vectors_of_the_reference_math(sp, cuda, name):
+    """Inputs and outputs produced by executing the reference's simple_attn (tests/golden/make_attn_golden.py)."""
+    import torch
+
+    g = np.load(os.path.join(GOLDEN, f"attn_simple_{name}.npz"))
+    q, k, v = (torch.from_numpy(g[n]).to(cuda)[None].contiguous() for n in ("q", "k", "v"))
+    o = sp.attn_fwd(q, k, v)
+    sp.status()
+    ok, worst = _close(o[0].cpu().numpy(), g["o"])
+    assert ok, f"max abs error {worst}"
+    o1 = sp.attn_fwd(q, k, v, scale=1.0)
+    sp.status()
+    ok, worst = _close(o1[0].cpu().numpy(), g["o_scale1"])
+    assert ok, f"max abs error {worst} (scale = 1)"
+
+
+def test_softmax_properties_at_larger_sizes(sp, orc, cuda):
+    """Sizes the CPU oracle cannot cover in full: (i) V = ones gives O = 1 exactly up to fp16 rounding of P's
+    row sums; (ii) attention is invariant to a permutation of the keys/values; (iii) sampled heads against
+    the oracle."""
+    import torch
+
+    BH, S, D = 8, 4096, 128
+    q, k, v = _qkv(sp, cuda, BH, S, D)
+    ones = torch.ones_like(v)
+    o = sp.attn_fwd(q, k, ones)
+    sp.status()
+    assert float((o.float() - 1.0).abs().max()) < 2e-3
+    perm = torch.randperm(S, device=cuda, generator=torch.Generator(device=cuda).manual_seed(5))
+    o_a = sp.attn_fwd(q, k, v)
+    o_b = sp.attn_fwd(q, k[:, perm].contiguous(), v[:, perm].contiguous())
+    sp.status()
+    assert float((o_a.float() - o_b.float()).abs().max()) < 2e-3
+    h = 5
+    _, ref = orc.attn_f16(q[h:h + 1, :].cpu().numpy(), k[h:h + 1].cpu().numpy(), v[h:h + 1].cpu().numpy())
+    ok, worst = _close(o_a[h:h + 1].cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+
+
+def test_large_scores_do_not_overflow(sp, orc, cuda):
+    """Scores far outside exp's range: the running-max rescaling must keep everything finite."""
+    BH, S, D = 1, 512, 64
+    q, k, v = _qkv(sp, cuda, BH, S, D)
+    o = sp.attn_fwd((q * 8).contiguous(), (k * 8).contiguous(), v, scale=1.0)
+    sp.status()
+    _, ref = orc.attn_f16((q * 8).cpu().numpy(), (k * 8).cpu().numpy(), v.cpu().numpy(), scale=1.0)
+    assert np.isfinite(o.float().cpu().numpy()).all()
+    ok, worst = _close(o.cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+
+
+def test_reference_shaped_host_entry_point(sp, orc, cuda):
+    """htod_f32_attn_sm100_fwd has the signature of htod_f32_tk_4090_fwd (tk_4090_fwd.hpp:7) and is called the
+    way torch_attn.py:40-57 calls it: host fp32 (N, d) arrays."""
+    N, d = 256, 64
+    g = np.load(os.path.join(GOLDEN, "attn_simple_n256_d64.npz"))
+    q, k, v = (np.ascontiguousarray(g[n].astype(np.float32)) for n in ("q", "k", "v"))
+    o = np.full((N, d), np.nan, dtype=np.float32)
+    f32p = ctypes.POINTER(ctypes.c_float)
+    sp.lib().htod_f32_attn_sm100_fwd(N, d, q.ctypes.data_as(f32p), k.ctypes.data_as(f32p), v.ctypes.data_as(f32p),
+                                     o.ctypes.data_as(f32p))
+    ok, worst = _close(o, g["o"])
+    assert ok, f"max abs error {worst}"
+
+
+def test_attention_argument_errors(sp, cuda):
+    import torch
+
+    L = sp.lib()
+    q = torch.zeros((1, 128, 64), dtype=torch.float16, device=cuda)
+    f = ctypes.c_float(0.125)
+    assert L.spork_attn_sm100_fwd_f16(1, 128, 96, q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), f, None) == 10002
+    assert L.spork_attn_sm100_fwd_f16(1, 128, 64, None, q.data_ptr(), q.data_ptr(), q.data_ptr(), f, None) == 10001
+    assert L.spork_attn_sm100_fwd_f16(1, 128, 64, q.data_ptr() + 2, q.data_ptr(), q.data_ptr(), q.data_ptr(), f,
+                                      None) == 10001
+    assert L.spork_attn_sm100_fwd_f16(0, 128, 64, None, None, None, None, f, None) == 0
+    assert sp.lib().spork_attn_sm100_supports(16, 4096, 128) == 1
+    assert sp.lib().spork_attn_sm100_supports(16, 4096, 80) == 0
+    sp.status()
