@@ -15,10 +15,12 @@
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
 // Per key block j and query tile w:
 //   S_w = Q_w K_j^T            tcgen05.mma, both operands K-major in shared memory
-//   softmax thread: row max, p = exp2((s - m) * scale*log2e), row sum; P_w (fp16)
-//       is written to shared memory in the 128B-swizzled K-major operand layout;
-//       when the running max moved, O_w is rescaled in place (tcgen05.ld/st)
-//   O_w += P_w V_j             tcgen05.mma, A = P_w (K-major), B = V_j (N-major)
+//   softmax thread: reads its whole S row into registers, row max,
+//       p = exp2((s - m) * scale*log2e), row sum; P_w (fp16, two per column) is
+//       written back into tensor memory over the first 64 columns of S_w;
+//       O_w is rescaled in place (tcgen05.ld/st) only when the row max grew by
+//       more than 2^8 since the last rescale (p then stays within fp16 range)
+//   O_w += P_w V_j             tcgen05.mma, A = P_w from tensor memory, B = V_j (N-major)
 // The two query tiles alternate, so the tensor core works on one tile while the
 // other tile's softmax runs.  Keys past the end of a ragged sequence are masked
 // to -inf; rows past the end are computed on zero-filled queries and not stored.
@@ -46,8 +48,9 @@ constexpr int kTileKV = 128;    // keys per block
 constexpr int kNumThreads = 320;
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kKvStages = 3;
+constexpr int kMaxKvStages = 8;
 constexpr int kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by more than 2^8
 
 template <int D>
 struct Config {
@@ -55,8 +58,9 @@ struct Config {
     static constexpr int kAtoms = D / 64;                      // 64-wide (128-byte) column blocks of a tile
     static constexpr int kTileBytes = kTileQ * D * 2;          // a Q, K or V tile
     static constexpr int kAtomBytes = 128 * 128;               // 128 rows x 128 bytes
-    static constexpr int kPBytes = kTileQ * kTileKV * 2;       // one P tile (fp16): 2 atoms
-    static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + kKvStages * kTileBytes + 2 * kPBytes + 1024;
+    static constexpr int kStagesFit = (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes;
+    static constexpr int kKvStages = kStagesFit > kMaxKvStages ? kMaxKvStages : kStagesFit;
+    static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + kKvStages * kTileBytes + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -71,8 +75,8 @@ struct Params {
 
 struct Barriers {
     uint64_t q_full;
-    uint64_t kv_full[kKvStages];
-    uint64_t kv_empty[kKvStages];
+    uint64_t kv_full[kMaxKvStages];
+    uint64_t kv_empty[kMaxKvStages];
     uint64_t s_full[2];
     uint64_t p_ready[2];
     uint64_t pv_done[2];
@@ -113,8 +117,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_smem = smem_base;                                  // 2 Q tiles
     const uint32_t kv_smem = q_smem + 2 * Cfg::kTileBytes;              // ring of K / V tiles
-    const uint32_t p_smem = kv_smem + kKvStages * Cfg::kTileBytes;      // 2 P tiles
-    Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (p_smem + 2 * Cfg::kPBytes - smem_u32(smem_raw)));
+    constexpr int kKvStages = Cfg::kKvStages;
+    Barriers* bars =
+        reinterpret_cast<Barriers*>(smem_raw + (kv_smem + kKvStages * Cfg::kTileBytes - smem_u32(smem_raw)));
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int head = blockIdx.x / p.q_pairs;
@@ -150,7 +155,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     // column offsets inside the allocation
-    const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128
+    const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128; P_w (fp16 pairs) reuses its first 64 columns
     const uint32_t tmem_o0 = tmem_base + 256;    // O_w at + w * 128
 
     if (warp == kLoadWarp) {
@@ -211,16 +216,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     umma_f16_ss<1>(tmem_s0 + w * 128, da, db, idesc_qk, kk != 0 ? 1u : 0u);
                 }
             };
-            // O_w (+)= P_w V from the V tile in ring slot `st`
+            // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
+            // B = the V tile in ring slot `st`
             auto issue_pv = [&](int w, uint32_t st, bool accumulate) {
-                const uint32_t pa = p_smem + w * Cfg::kPBytes;
                 const uint32_t vb = kv_smem + st * Cfg::kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < kTileKV / 16; ++kk) {
-                    const uint64_t da = umma_desc_kmajor_sw128(pa + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
                     // 16 keys = 16 rows of 128 bytes further down the V tile; d-halves are one atom apart
                     const uint64_t db = umma_desc_mnmajor_sw128(vb + kk * 16 * 128, Cfg::kAtomBytes, 1024);
-                    umma_f16_ss<1>(tmem_o0 + w * 128, da, db, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
+                    umma_f16_ts<1>(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, db, idesc_pv,
+                                   (accumulate || kk != 0) ? 1u : 0u);
                 }
             };
             do {
@@ -261,7 +266,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         }
                         tcgen05_fence_after();
                         issue_pv(w, v_stage, j > 0);
-                        umma_commit<1>(smem_u32(&bars->pv_done[w]));
+                        if (!more) {
+                            umma_commit<1>(smem_u32(&bars->pv_done[w]));  // completes once: O_w is final
+                        }
                         if (w == 1) {
                             umma_commit<1>(smem_u32(&bars->kv_empty[v_stage]));
                         }
@@ -290,10 +297,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t lane_addr = (quarter * 32u) << 16;
         const uint32_t tmem_s = tmem_s0 + w * 128 + lane_addr;
         const uint32_t tmem_o = tmem_o0 + w * 128 + lane_addr;
-        // this row inside a P atom: 8-row groups of 1024 bytes, 16-byte chunks XORed with (row & 7)
-        const uint32_t p_row = p_smem + w * Cfg::kPBytes + (row >> 3) * 1024 + (row & 7) * 128;
         const float sl2 = p.scale_log2e;
-        float m_run = -INFINITY;  // running row max (raw scores)
+        float m_ref = -INFINITY;  // row max the stored O and l are relative to (raw scores)
         float l_run = 0.0f;       // running row sum
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
@@ -304,97 +309,79 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 ok = false;
                 break;
             }
+            // s_full also means every earlier MMA of the issuing thread is complete: P_w of the previous
+            // block has been consumed and O_w is not being written.
             tcgen05_fence_after();
-            const int valid = p.S - j * kTileKV;  // keys of this block that exist
-            const bool ragged = valid < kTileKV;  // uniform over the CTA
-            // pass 1: row max
-            float m_blk = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kTileKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_s + c * 32, r);
+            uint32_t r[128];
+            {
+                uint32_t(&r0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
+                uint32_t(&r1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
+                uint32_t(&r2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[64]);
+                uint32_t(&r3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[96]);
+                tmem_ld_32x32b_x32(tmem_s, r0);
+                tmem_ld_32x32b_x32(tmem_s + 32, r1);
+                tmem_ld_32x32b_x32(tmem_s + 64, r2);
+                tmem_ld_32x32b_x32(tmem_s + 96, r3);
                 tmem_ld_wait();
+            }
+            const int valid = p.S - j * kTileKV;  // keys of this block that exist
+            if (valid < kTileKV) {                // uniform over the CTA
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (i >= valid) {
+                        r[i] = 0xFF800000u;  // -inf
+                    }
+                }
+            }
+            float m_blk = __uint_as_float(r[0]);
+#pragma unroll
+            for (int i = 1; i < 128; ++i) {
+                m_blk = fmaxf(m_blk, __uint_as_float(r[i]));
+            }
+            // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
+            const bool grow = j == 0 || (m_blk - m_ref) * sl2 > kRescaleThreshold;
+            float alpha = 1.0f;
+            if (grow) {
+                alpha = ex2_approx((m_ref - m_blk) * sl2);  // 0 on the first block
+                m_ref = m_blk;
+            }
+            const float neg_m = -m_ref * sl2;
+            float l_blk0 = 0.0f, l_blk1 = 0.0f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]);
-                    if (ragged && c * 32 + i >= valid) {
-                        s = -INFINITY;
-                    }
-                    m_blk = fmaxf(m_blk, s);
-                }
-            }
-            const float m_new = fmaxf(m_run, m_blk);
-            const float alpha = ex2_approx((m_run - m_new) * sl2);  // 0 on the first block (m_run = -inf)
-            const float neg_m = -m_new * sl2;
-            // The previous P_w V MMA must be done before P_w is overwritten and O_w touched.
-            if (j > 0) {
-                if (!mbar_wait(smem_u32(&bars->pv_done[w]), (uint32_t)((j - 1) & 1), abort_flag)) {
-                    if (lane == 0) {
-                        report_timeout(p, abort_flag, 3, 0x20 + w);
-                    }
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after();
-            }
-            // pass 2: p = exp2(s * sl2 - m * sl2), row sum, P (fp16) to shared memory
-            float l_blk = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < kTileKV / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_s + c * 32, r);
-                tmem_ld_wait();
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float s0 = __uint_as_float(r[2 * i]);
-                    float s1 = __uint_as_float(r[2 * i + 1]);
-                    if (ragged) {
-                        if (c * 32 + 2 * i >= valid) {
-                            s0 = -INFINITY;
-                        }
-                        if (c * 32 + 2 * i + 1 >= valid) {
-                            s1 = -INFINITY;
-                        }
-                    }
-                    const float p0 = ex2_approx(fmaf(s0, sl2, neg_m));
-                    const float p1 = ex2_approx(fmaf(s1, sl2, neg_m));
-                    l_blk += p0 + p1;
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[half * 64 + 2 * i]), sl2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[half * 64 + 2 * i + 1]), sl2, neg_m));
+                    l_blk0 += p0;
+                    l_blk1 += p1;
                     packed[i] = pack_half2(p0, p1);
                 }
-                // columns [32c, 32c+32) = atom c/2, 16-byte chunks (c%2)*4 .. +3
-                const uint32_t atom_addr = p_row + (c >> 1) * Cfg::kAtomBytes;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t chunk = (uint32_t)((c & 1) * 4 + q4);
-                    st_shared_v4(atom_addr + ((chunk ^ (row & 7u)) << 4), packed[4 * q4], packed[4 * q4 + 1],
-                                 packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                tmem_st_32x32b_x32(tmem_s + half * 32, packed);
             }
-            l_run = l_run * alpha + l_blk;
-            m_run = m_new;
-            // rescale O_w when some row of this warp moved its max (never on the first block: O is not yet written)
-            if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+            l_run = l_run * alpha + (l_blk0 + l_blk1);
+            // rescale O_w when some row of this warp moved its reference max (never on the first block)
+            if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
 #pragma unroll 1
-                for (int c = 0; c < D / 16; ++c) {
-                    uint32_t r[16];
-                    tmem_ld_32x32b_x16(tmem_o + c * 16, r);
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32b_x32(tmem_o + c * 32, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    for (int i = 0; i < 32; ++i) {
+                        o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                     }
-                    tmem_st_32x32b_x16(tmem_o + c * 16, r);
+                    tmem_st_32x32b_x32(tmem_o + c * 32, o);
                 }
-                tmem_st_wait();
             }
-            fence_proxy_async_smem();  // P stores -> visible to the MMA's shared-memory reads
+            tmem_st_wait();
             tcgen05_fence_before();
             mbar_arrive(smem_u32(&bars->p_ready[w]));
         }
         // ---- epilogue: O_w / l -> fp16 -> global
         if (ok) {
-            if (!mbar_wait(smem_u32(&bars->pv_done[w]), (uint32_t)((n_blocks - 1) & 1), abort_flag)) {
+            if (!mbar_wait(smem_u32(&bars->pv_done[w]), 0u, abort_flag, 20)) {
                 if (lane == 0) {
                     report_timeout(p, abort_flag, 3, 0x28 + w);
                 }
