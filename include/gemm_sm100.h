@@ -1,0 +1,68 @@
+// C++ face of the sm_100a GEMM for the reference harness: the same by-value
+// descriptor and launch-function shapes as gemm/gpu_tensor.h:9-21 (GPU_Tensors),
+// gemm/gemm_sm90.h:14 (matmul_sm90) and gemm/gemm_sm80.h:5-6 (matmul_sm80,
+// matmul_sm80_supports), with fp16 operands.  Header-only over the C ABI.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "spork_b200.h"
+
+struct GPU_TensorsF16
+{
+    uint32_t M;
+    uint32_t N;
+    uint32_t K;
+    __half const *a; /* pointer to GPU memory, M x K */
+    __half const *b; /* pointer to GPU memory, N x K when b_col_major */
+    float *c;        /* pointer to GPU memory, M x N */
+
+    bool a_col_major;
+    bool b_col_major;
+    bool c_col_major;
+};
+
+// K split modes the sm_100a kernel offers; output_stationary and split_k_outer
+// have the meaning of gemm_sm90_k_mode (gemm/gemm_sm90.h:5-12).
+enum class gemm_sm100_k_mode
+{
+    output_stationary,
+    split_k_outer,
+};
+
+// The kernel takes the harness's hot layout only: A row-major, B stored N x K,
+// C row-major (gemm/gemm_test.cu:365); K must be a multiple of 8.
+inline bool matmul_sm100_supports(GPU_TensorsF16 t)
+{
+    return !t.a_col_major && t.b_col_major && !t.c_col_major && spork_gemm_sm100_supports(t.M, t.N, t.K) != 0;
+}
+
+// Asynchronous on `stream`, like matmul_sm90.  Errors are printed, as the
+// reference's launchers do, and also returned.
+inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode k_mode = gemm_sm100_k_mode::output_stationary,
+                        int split_k = 1, int variant = 0)
+{
+    if (!matmul_sm100_supports(t)) {
+        fprintf(stderr, "matmul_sm100: unsupported layout or K %% 8 != 0 (M=%u N=%u K=%u)\n", t.M, t.N, t.K);
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    int rc;
+    if (k_mode == gemm_sm100_k_mode::split_k_outer && split_k > 1) {
+        const int block_n = variant ? variant : (t.N <= 64 ? 64 : (t.N <= 128 ? 128 : 256));
+        rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, 2, split_k, 0, stream);
+    } else {
+        rc = spork_gemm_sm100_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, variant, stream);
+    }
+    if (rc != 0) {
+        fprintf(stderr, "matmul_sm100: error %d\n", rc);
+    }
+    return rc;
+}
+
+inline int matmul_baseline_f16(GPU_TensorsF16 t, cudaStream_t stream)
+{
+    return spork_gemm_baseline_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, stream);
+}

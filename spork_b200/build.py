@@ -54,5 +54,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_harness() -> str:
+    """Link the C++ benchmark/correctness harness (csrc/main_gemm.cpp) against the library and cuBLAS."""
+    build()
+    exe = os.path.join(HERE, "bin", "gemm")
+    os.makedirs(os.path.dirname(exe), exist_ok=True)
+    src = os.path.join(CSRC, "main_gemm.cpp")
+    if _stale(exe, [src, LIB, os.path.join(HERE, "..", "include", "gemm_sm100.h")]):
+        cmd = [NVCC, "-std=c++17", "-O2", "-x", "cu", src, "-o", exe, "-L", HERE, "-lspork_b200", "-lcublas",
+               "-Xlinker", "-rpath=$ORIGIN/.."]
+        subprocess.run(cmd, check=True)
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--harness" in sys.argv:
+        print(build_harness())
