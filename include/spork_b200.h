@@ -89,7 +89,10 @@ int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K, const voi
  * measured best).  stages: shared-memory ring depth, 0 = as deep as fits;
  * group_m: m-tiles per raster group, 0 = default; l2_hints: bit 0 = A loads
  * evict-last, bit 1 = B loads evict-last, bit 2 = B loads evict-first;
- * backoff_ns: sleep between polls of the long waits, 0 = spin.  The reference
+ * backoff_ns: sleep between polls of the long waits, 0 = spin.  Bits 4..6 of
+ * l2_hints switch diagnostic experiments whose RESULTS ARE UNDEFINED (0x10 the
+ * epilogue drops its stores, 0x20 the producer stops loading after the first
+ * ring fill, 0x40 stores go straight from registers).  The reference
  * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
 int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);
 

@@ -87,6 +87,9 @@ struct Params {
     uint32_t group_m;            // raster: m-tiles per group
     uint32_t l2_hints;           // bit 0: A loads evict_last, bit 1: B loads evict_last, bit 2: B loads evict_first
     uint32_t backoff_ns;         // sleep between polls of the long (epilogue / producer) waits; 0 = spin
+    uint32_t experiment;         // diagnostics only, results undefined: bit 0 = epilogue drops its stores,
+                                 // bit 1 = producer stops issuing loads once the ring has been filled once,
+                                 // bit 2 = epilogue stores straight from registers (no shared-memory staging)
     float* C;
     uint32_t* status;            // device status word
 };
@@ -195,7 +198,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             const uint64_t pol_a = (p.l2_hints & 1u) ? l2_policy_evict_last() : l2_policy_evict_normal();
             const uint64_t pol_b = (p.l2_hints & 2u) ? l2_policy_evict_last()
@@ -213,7 +216,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
                     const uint32_t sb = sa + Cfg::kABytes;
                     const uint32_t full = smem_u32(&bars->full[stage]);
-                    if (CG == 1) {
+                    if ((p.experiment & 2u) && issued >= p.stages) {
+                        if (is_leader) {
+                            mbar_arrive(full);  // hand the stale stage over without loading
+                        }
+                    } else if (CG == 1) {
                         mbar_arrive_expect_tx(full, Cfg::kStageBytes);
                         tma_load_2d_hint(sa, &tmap_a, full, (int32_t)(kb * kBlockK), a_row, pol_a);
                         tma_load_2d_hint(sb, &tmap_b, full, (int32_t)(kb * kBlockK), b_row, pol_b);
@@ -226,6 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         tma_load_2d_pair_hint(sa, &tmap_a, leader_full, (int32_t)(kb * kBlockK), a_row, pol_a);
                         tma_load_2d_pair_hint(sb, &tmap_b, leader_full, (int32_t)(kb * kBlockK), b_row, pol_b);
                     }
+                    ++issued;
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
@@ -319,8 +327,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tmem_ld_32x32b_x32(taddr0 + c * kEpiCols, r);
                 tmem_ld_wait();
                 const uint32_t col = col0 + c * kEpiCols;
-                if (!rows_live || col >= p.N) {
+                if (!rows_live || col >= p.N || (p.experiment & 1u)) {
                     continue;  // warp-uniform
+                }
+                if (!kWorkspace && (p.experiment & 4u)) {
+                    // straight from registers: every thread writes the 128 contiguous bytes of its row
+                    const uint32_t row = row0 + lane;
+                    if (row < p.M && col + 32 <= p.N) {
+                        float4* dst = reinterpret_cast<float4*>(p.C + (size_t)row * p.N + col);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        }
+                    }
+                    continue;
                 }
                 if (kWorkspace || p.use_tma_store) {
                     const uint32_t slab = slab0 + slab_sel * kSlabBytes;
@@ -442,6 +463,7 @@ struct Tuning {
     int group_m = 8;
     int l2_hints = 0;
     int backoff_ns = 0;
+    int experiment = 0;
 };
 static Tuning g_tuning;
 
@@ -482,6 +504,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     p.group_m = tune.group_m >= 1 ? (uint32_t)tune.group_m : (uint32_t)kGroupM;
     p.l2_hints = (uint32_t)tune.l2_hints;
     p.backoff_ns = (uint32_t)tune.backoff_ns;
+    p.experiment = (uint32_t)tune.experiment;
 
     CUtensorMap tmap_a, tmap_b, tmap_c;
     int rc = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, M, K, kBlockM, kBlockK);
@@ -653,6 +676,7 @@ static int launch_static(uint32_t M, uint32_t N, uint32_t K, const void* A, cons
     p.group_m = (uint32_t)kGroupM;
     p.l2_hints = 0;
     p.backoff_ns = 0;
+    p.experiment = 0;
 
     const uint32_t pitch = (N + 3u) & ~3u;  // rows of the workspace are multiples of 16 bytes
     if ((size_t)p.split_k * M * pitch * sizeof(float) > kStaticWorkspaceBytes) {
@@ -821,9 +845,11 @@ extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 7 || backoff_ns < 0 || backoff_ns > 100000) {
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x7F || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
+    spork::gemm_sm100::g_tuning.experiment = l2_hints >> 4;  // bits 4..6: diagnostic experiments (see Params)
+    l2_hints &= 7;
     spork::gemm_sm100::g_tuning.stages = stages;
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
     spork::gemm_sm100::g_tuning.l2_hints = l2_hints;
