@@ -119,13 +119,59 @@ def cpu_sample(oracle, rows, a_rows=None, b=None):
     return 2.0 * rows * N_DIM * K_DIM / dt / 1e12, dt, a_rows, b
 
 
+def other_configs(sp, torch, dev, peaks):
+    """The remaining single-GPU configurations, measured briefly (25 launches, mean of the middle 13, the
+    reference's protocol, gemm/gemm_test.cu:394-405): the skinny-N sweep in HBM GB/s and the attention forward."""
+
+    def iqr_ms(fn, n=25):
+        for _ in range(3):
+            fn()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        ev[0].record()
+        for i in range(n):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        ts = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(n))
+        mid = ts[n // 4: n // 4 + (n + 1) // 2]
+        return sum(mid) / len(mid)
+
+    out = {}
+    M, K = 16384, 8192
+    a = torch.empty((M, K), dtype=torch.float16, device=dev)
+    sp.init_test_data(a, sp.DATA_UNIFORM_PM1, sp.SEED_A)
+    for n in (64, 128, 256):
+        b = torch.empty((n, K), dtype=torch.float16, device=dev)
+        sp.init_test_data(b, sp.DATA_UNIFORM_PM1, sp.SEED_B, transpose_rule=True)
+        c = torch.empty((M, n), dtype=torch.float32, device=dev)
+        ms = iqr_ms(lambda: sp.matmul_sm100(a, b, c))
+        nbytes = 2 * M * K + 2 * n * K + 4 * M * n
+        out[f"gemm_M16384_N{n}_K8192"] = {"ms": ms, "tflops": 2.0 * M * n * K / ms / 1e9, "hbm_gbs": nbytes / ms / 1e6,
+                                          "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del a
+    BH, S, D = 256, 4096, 128
+    qkv = []
+    for seed in (101, 101 ^ 888, 101 ^ 1776):
+        t = torch.empty((BH * S, D), dtype=torch.float16, device=dev)
+        sp.init_test_data(t, sp.DATA_NORMAL, seed)
+        qkv.append(t.view(BH, S, D))
+    o = torch.empty_like(qkv[0])
+    ms = iqr_ms(lambda: sp.attn_fwd(qkv[0], qkv[1], qkv[2], o), n=15)
+    flops = 4.0 * BH * S * S * D
+    out["attention_B16_H16_S4096_D128"] = {"ms": ms, "tflops": flops / ms / 1e9,
+                                            "frac_of_measured_bf16_burst": flops / ms / 1e9 / peaks["bf16_tflops"],
+                                            "frac_of_nominal_2250": flops / ms / 1e9 / 2250.0}
+    sp.status()
+    return out
+
+
 def run_reference(args, rank, world):
     """The reference arm: the reference's CPU GEMM (restated in oracle/) on this box's host cores."""
     if rank != 0:
         return
     from oracle import oracle
 
-    threads = oracle.num_threads()
+    threads = oracle.use_all_cores()
     # size a step so that the whole run takes a couple of minutes at most
     tf, dt, a_rows, b = cpu_sample(oracle, 64)
     step_target_s = min(2.0, 60.0 / (args.steps + args.warmup))  # the whole run stays near a minute
@@ -279,6 +325,7 @@ def main():
         return
 
     peaks = measured_peaks()
+    other = other_configs(sp, torch, dev, peaks) if world == 1 else None
     avg_launch_ms = sum(launch_ms) / len(launch_ms)
     achieved = FLOPS_PER_STEP / (avg_launch_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
@@ -292,6 +339,7 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         from oracle import oracle
 
+        oracle.use_all_cores()
         tf, dt, a_rows, b_host = cpu_sample(oracle, 64)
         rows = int(max(64, min(M_PER_RANK, (12.0 / max(dt, 1e-6)) * 64)))  # about 12 s of CPU work
         rows -= rows % 64
@@ -306,6 +354,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM,
                     "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
             "gpu_launches": args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "other_configs": other,
             "context": {"cublas_fp16_tflops_same_protocol": cublas_tflops, "frac_of_nominal_fp16_peak": value / (2250.0 * world)}}
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.spork_oracle_attn_f16.restype = ctypes.c_int
         L.spork_oracle_attn_f16.argtypes = [ctypes.c_int] * 3 + [u16p, u16p, u16p, u16p, f32p, ctypes.c_float]
         L.spork_oracle_num_threads.restype = ctypes.c_int
+        L.spork_oracle_set_threads.argtypes = [ctypes.c_int]
+        L.spork_oracle_set_threads.restype = None
         _lib = L
     return _lib
 
@@ -91,6 +93,13 @@ def _as_bits(a: np.ndarray) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().spork_oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says; returns the thread count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().spork_oracle_set_threads(n)
+    return num_threads()
 
 
 def pcg3d(x: int, y: int, z: int) -> int:

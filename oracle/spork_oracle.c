@@ -453,6 +453,18 @@ ORACLE_API int spork_oracle_attn_f16(int BH, int S, int D, const uint16_t* q, co
     return failed;
 }
 
+/* Number of OpenMP threads later calls use (launchers often export OMP_NUM_THREADS=1). */
+ORACLE_API void spork_oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n >= 1) {
+        omp_set_num_threads(n);
+    }
+#else
+    (void)n;
+#endif
+}
+
 ORACLE_API int spork_oracle_num_threads(void)
 {
 #ifdef _OPENMP

@@ -17,7 +17,7 @@
 //     so the epilogue of tile i overlaps the main loop of tile i+1;
 //   * cta_group::2: a pair of CTAs on neighbouring SMs computes a 256 x block_n
 //     tile with one MMA stream issued by the pair's leader.  Each CTA loads its
-//     own 128 rows of A and its own half of the B tile - no multicast - and the
+//     own 128 rows of A and its own half of the B tile with plain unicast loads, and the
 //     MMA reads B from both CTAs' shared memory;
 //   * epilogue: tcgen05.ld (one thread per accumulator row, 32 columns at a
 //     time) -> 128B-swizzled staging slab in shared memory -> TMA store (or TMA
