@@ -165,6 +165,60 @@ def other_configs(sp, torch, dev, peaks):
     return out
 
 
+def run_attention(args, sp, torch, dist, dev, rank, world):
+    """Attention forward, batch 16 x 16 heads, S = 4096, D = 128, the 256 (batch, head) slices dealt out in
+    contiguous blocks over the ranks (strong scaling: the total problem is fixed).  One step = one launch on
+    this rank's heads."""
+    from spork_b200.sharding import head_slab
+
+    BH_TOTAL, S, D = 256, 4096, 128
+    slab = head_slab(BH_TOTAL, rank, world)
+    qkv = []
+    for seed in (101, 101 ^ 888, 101 ^ 1776):
+        t = torch.empty((slab.count * S, D), dtype=torch.float16, device=dev)
+        sp.init_test_data(t, sp.DATA_NORMAL, seed, row0=slab.start * S)
+        qkv.append(t.view(slab.count, S, D))
+    o = torch.empty_like(qkv[0])
+    for _ in range(args.warmup):
+        sp.attn_fwd(qkv[0], qkv[1], qkv[2], o)
+    sp.status()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(dev.index) as clocks:
+        events[0].record()
+        for i in range(args.steps):
+            sp.attn_fwd(qkv[0], qkv[1], qkv[2], o)
+            events[i + 1].record()
+        torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sp.status()
+    t = torch.tensor([events[0].elapsed_time(events[-1])], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return
+    ms_per_step = float(t.item()) / args.steps
+    flops = 4.0 * BH_TOTAL * S * S * D
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    peaks = measured_peaks()
+    print(json.dumps({"metric": "attention forward TFLOP/s (B=16 H=16 S=4096 D=128, fp16, non-causal)", "value": value,
+                      "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                      "dtype": "f16 in, f32 softmax, f16 out", "data": "synthetic",
+                      "config": {"workload": "attention forward BH=256 S=4096 D=128, heads sharded over ranks",
+                                 "values": "unit normal from a position hash, seeds 101, 101^888, 101^1776",
+                                 "l2": "inputs exceed L2: Q,K,V,O = 1 GiB"},
+                      "clocks": clocks.summary(), "gpu_launches": args.steps,
+                      "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
+                                   "unit": UNIT, "frac": value / world / peaks["bf16_tflops"], "traffic": None,
+                                   "kernel": "spork::attn_sm100::attn_fwd_kernel<128>",
+                                   "frac_of_nominal_2250": value / world / 2250.0}}), flush=True)
+
+
 def run_reference(args, rank, world):
     """The reference arm: the reference's CPU GEMM (restated in oracle/) on this box's host cores."""
     if rank != 0:
@@ -204,6 +258,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (N=1 runs it by default)")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "attention"],
+                    help="gemm = the headline line; attention = the companion forward kernel, heads sharded over ranks")
     ap.add_argument("--kernel-only", action="store_true",
                     help="profiling runs: only the warm-up and timed launches (no end-to-end, library or CPU legs)")
     args = ap.parse_args()
@@ -231,6 +287,12 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "attention":
+        run_attention(args, sp, torch, dist, dev, rank, world)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- operands: this rank's slab of A, a replica of B (made on rank 0, broadcast over NVLink)
     a = torch.empty((M_PER_RANK, K_DIM), dtype=torch.float16, device=dev)

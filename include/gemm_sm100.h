@@ -62,6 +62,34 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
     return rc;
 }
 
+// Drop-in for the reference's own descriptor type: `Tensors` is any by-value struct with the fields of
+// GPU_Tensors (gemm/gpu_tensor.h:9-21: M, N, K, float const* a, b, float* c, a_col_major, b_col_major,
+// c_col_major), so `matmul_sm100_tf32(t, stream)` can stand where `matmul_sm90(t, mode, stream)`
+// (gemm/gemm_sm90.h:14) or `matmul_sm80(t, stream)` (gemm/gemm_sm80.h:5) stands.  Operands are read as
+// tf32, as those kernels read them.  Like matmul_sm90 it takes A row-major and B stored N x K
+// (gemm/gemm_sm90.cu:1269-1270); a column-major C is produced by exchanging the operands.
+template <class Tensors>
+inline bool matmul_sm100_tf32_supports(Tensors t)
+{
+    return !t.a_col_major && t.b_col_major && t.K % 4 == 0;
+}
+
+template <class Tensors>
+inline int matmul_sm100_tf32(Tensors t, cudaStream_t stream, int split_k = 1)
+{
+    if (!matmul_sm100_tf32_supports(t)) {
+        fprintf(stderr, "matmul_sm100_tf32: unsupported layout or K %% 4 != 0 (M=%u N=%u K=%u)\n", t.M, t.N, t.K);
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    // C^T = B A^T: a column-major M x N result is the row-major N x M result of the exchanged product
+    const int rc = t.c_col_major ? spork_gemm_sm100_tf32f32(t.N, t.M, t.K, t.b, t.a, t.c, 0, split_k, stream)
+                                 : spork_gemm_sm100_tf32f32(t.M, t.N, t.K, t.a, t.b, t.c, 0, split_k, stream);
+    if (rc != 0) {
+        fprintf(stderr, "matmul_sm100_tf32: error %d\n", rc);
+    }
+    return rc;
+}
+
 inline int matmul_baseline_f16(GPU_TensorsF16 t, cudaStream_t stream)
 {
     return spork_gemm_baseline_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, stream);

@@ -53,6 +53,15 @@ int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K);
 int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int variant,
                             void* stream);
 
+/* The same kernel on the reference's own operand type: fp32 A and B read as tf32
+ * by the tensor cores (tcgen05.mma.kind::tf32), fp32 accumulation and output -
+ * what matmul_sm90 / matmul_sm80 / cublasSgemm-in-TF32-mode compute
+ * (gemm/gemm_sm90.cu:555-614, gemm/gemm_sm80.cu:92-101, gemm/gemm_test.cu:208).
+ * Same layout (A MxK, B NxK, C MxN, all row-major); K % 4 == 0.  split_k >= 1
+ * as in the _ex entry point. */
+int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
+                             int variant, int split_k, void* stream);
+
 /* Launch with every tunable explicit (benchmark sweeps and tests).
  *   block_n   64 / 128 / 256   output-tile width
  *   cta_group 1 = one CTA per tile (128 x block_n),

@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
         L.spork_oracle_gemm_f16f32.argtypes = [ctypes.c_uint32] * 3 + [u16p, u16p, f32p]
         L.spork_oracle_gemm_f16f64.restype = ctypes.c_int
         L.spork_oracle_gemm_f16f64.argtypes = [ctypes.c_uint32] * 3 + [u16p, u16p, f64p]
+        L.spork_oracle_gemm_f32.restype = ctypes.c_int
+        L.spork_oracle_gemm_f32.argtypes = [ctypes.c_uint32] * 3 + [f32p, f32p, f32p, ctypes.c_int]
         L.spork_oracle_gemm_f16f32_rows.restype = ctypes.c_int
         L.spork_oracle_gemm_f16f32_rows.argtypes = [ctypes.c_uint32] * 3 + [u16p, u16p, ctypes.c_uint32,
                                                                              ctypes.c_uint32, f32p]
@@ -126,6 +128,20 @@ def gemm_f16f32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
         rc = lib().spork_oracle_gemm_f16f32(M, N, K, _u16(A), _u16(B), _f32(C))
         if rc:
             raise MemoryError("oracle gemm allocation failed")
+    return C
+
+
+def gemm_f32(a: np.ndarray, b: np.ndarray, tf32_mode: int = 0) -> np.ndarray:
+    """fp32 operands (the reference's type): C = A . B^T, fp32 accumulation, k ascending.
+    tf32_mode 0 = plain fp32, 1 = operands truncated to tf32, 2 = operands rounded to tf32."""
+    A = np.ascontiguousarray(a, dtype=np.float32)
+    B = np.ascontiguousarray(b, dtype=np.float32)
+    M, K = A.shape
+    N, K2 = B.shape
+    assert K == K2
+    C = np.zeros((M, N), dtype=np.float32)
+    if M and N:
+        lib().spork_oracle_gemm_f32(M, N, K, _f32(A), _f32(B), _f32(C), tf32_mode)
     return C
 
 

@@ -286,6 +286,45 @@ ORACLE_API int spork_oracle_gemm_f16f32(uint32_t M, uint32_t N, uint32_t K, cons
     return failed;
 }
 
+/* The reference's own operand type: fp32 A (M x K) and B (stored N x K), fp32 accumulation, k ascending -
+ * nyc25_gemm_cpu (docs/nyc25.py:13-56) on the harness layout.  tf32_mode says what happens to the operands
+ * before the multiply: 0 = nothing (plain fp32, what gemm/gemm_baseline.cu computes), 1 = the low 13
+ * mantissa bits are dropped (truncation to tf32), 2 = rounded to tf32, nearest with ties away from zero
+ * (cvt.rna.tf32.f32).  tf32 x tf32 products are exact in fp32. */
+static inline float to_tf32(float x, int mode)
+{
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if (mode == 2 && (u & 0x7F800000u) != 0x7F800000u) {
+        u += 0x1000u;
+    }
+    if (mode != 0) {
+        u &= 0xFFFFE000u;
+    }
+    memcpy(&x, &u, 4);
+    return x;
+}
+
+ORACLE_API int spork_oracle_gemm_f32(uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
+                                     int tf32_mode)
+{
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t m = 0; m < (int64_t)M; ++m) {
+        for (uint32_t n = 0; n < N; ++n) {
+            float acc = 0.0f;
+            for (uint32_t k = 0; k < K; ++k) {
+                /* the product is formed exactly (double) and rounded once to fp32, as an FMA would not
+                 * round it at all for tf32 operands and as fp32 multiply does for plain operands */
+                const float a = to_tf32(A[(size_t)m * K + k], tf32_mode);
+                const float b = to_tf32(B[(size_t)n * K + k], tf32_mode);
+                acc = tf32_mode ? (float)((double)acc + (double)a * (double)b) : acc + a * b;
+            }
+            C[(size_t)m * N + n] = acc;
+        }
+    }
+    return 0;
+}
+
 /* Same contraction with fp64 accumulation: bounds the oracle's own rounding. */
 ORACLE_API int spork_oracle_gemm_f16f64(uint32_t M, uint32_t N, uint32_t K, const uint16_t* A, const uint16_t* B,
                                         double* C)

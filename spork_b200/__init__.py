@@ -25,6 +25,7 @@ from .api import (  # noqa: F401
     matmul_sm100,
     matmul_sm100_htod,
     matmul_sm100_supports,
+    matmul_sm100_tf32,
     status,
     tune,
     version,

@@ -61,6 +61,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_supports.restype = i32
         L.spork_gemm_sm100_f16f32.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
         L.spork_gemm_sm100_f16f32.restype = i32
+        L.spork_gemm_sm100_tf32f32.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, vp]
+        L.spork_gemm_sm100_tf32f32.restype = i32
         L.spork_gemm_sm100_f16f32_ex.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, i32, i32, vp]
         L.spork_gemm_sm100_f16f32_ex.restype = i32
         L.spork_gemm_sm100_f16f32_static.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
@@ -153,6 +155,23 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
             bn = block_n if block_n is not None else (variant or (64 if N <= 64 else 128 if N <= 128 else 256))
             rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cta_group or 2, split_k, max_ctas, sp)
     _check(rc, "spork_gemm_sm100_f16f32")
+    return c
+
+
+def matmul_sm100_tf32(a, b, c=None, *, variant: int = 0, split_k: int = 1, stream=None):
+    """c[M,N] = a[M,K] @ b[N,K]^T with fp32 operands read as tf32 (the reference's own operand type)."""
+    import torch
+
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if c is None:
+        c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    pa, pb, pc = (_dev_ptr(t, torch.float32, n) for t, n in ((a, "a"), (b, "b"), (c, "c")))
+    with torch.cuda.device(a.device):
+        rc = lib().spork_gemm_sm100_tf32f32(M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
+    _check(rc, "spork_gemm_sm100_tf32f32")
     return c
 
 

@@ -47,6 +47,10 @@ using namespace ptx;
 constexpr int kBlockM = 128;        // rows of A (and of the accumulator) per CTA
 constexpr int kBlockK = 64;         // fp16 elements along K per stage: one 128-byte swizzle atom
 constexpr int kUmmaK = 16;          // K of one tcgen05.mma.kind::f16
+// fp32 operands read as tf32 (the reference's own operand type, gemm/gpu_tensor.h:14-16): the same
+// 128-byte rows hold 32 elements, one tcgen05.mma.kind::tf32 covers K = 8, so the byte layout of a
+// stage, the descriptors and the four MMAs per stage are identical.
+constexpr int kBlockKTf32 = 32;
 constexpr int kNumThreads = 192;    // 6 warps
 constexpr int kEpilogueWarp0 = 2;   // warps 2..5
 constexpr int kNumEpilogueWarps = 4;
@@ -140,7 +144,7 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
 // kWorkspace = true: each K split stores its partial tile into slab `split` of a
 // [split][M][N] fp32 workspace (tmap_c is then a 3-D map over it) instead of
 // writing or reduce-adding into C; a second kernel sums the slabs in a fixed order.
-template <int CG, int BLOCK_N, bool kWorkspace = false>
+template <int CG, int BLOCK_N, bool kWorkspace = false, bool kTf32 = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_c, const Params p)
@@ -194,6 +198,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const uint32_t tmem_base = bars->tmem_base;
 
     const uint32_t num_items = p.tiles_m * p.tiles_n * p.split_k;
+    constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;  // elements along K per stage
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -222,16 +227,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     } else if (CG == 1) {
                         mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-                        tma_load_2d_hint(sa, &tmap_a, full, (int32_t)(kb * kBlockK), a_row, pol_a);
-                        tma_load_2d_hint(sb, &tmap_b, full, (int32_t)(kb * kBlockK), b_row, pol_b);
+                        tma_load_2d_hint(sa, &tmap_a, full, (int32_t)(kb * kElemsK), a_row, pol_a);
+                        tma_load_2d_hint(sb, &tmap_b, full, (int32_t)(kb * kElemsK), b_row, pol_b);
                     } else {
                         // Both CTAs' bytes complete on the leader's barrier.
                         if (is_leader) {
                             mbar_arrive_expect_tx(full, Cfg::kStageBytes * 2);
                         }
                         const uint32_t leader_full = map_to_cta(full, 0);
-                        tma_load_2d_pair_hint(sa, &tmap_a, leader_full, (int32_t)(kb * kBlockK), a_row, pol_a);
-                        tma_load_2d_pair_hint(sb, &tmap_b, leader_full, (int32_t)(kb * kBlockK), b_row, pol_b);
+                        tma_load_2d_pair_hint(sa, &tmap_a, leader_full, (int32_t)(kb * kElemsK), a_row, pol_a);
+                        tma_load_2d_pair_hint(sb, &tmap_b, leader_full, (int32_t)(kb * kElemsK), b_row, pol_b);
                     }
                     ++issued;
                     if (++stage == p.stages) {
@@ -244,7 +249,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0 && is_leader) {
-            constexpr uint32_t idesc = umma_idesc_f16_f32(Cfg::kUmmaM, Cfg::kUmmaN);
+            constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32_f32(Cfg::kUmmaM, Cfg::kUmmaN)
+                                             : umma_idesc_f16_f32(Cfg::kUmmaM, Cfg::kUmmaN);
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
@@ -272,8 +278,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                     for (int k = 0; k < kBlockK / kUmmaK; ++k) {
                         // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the (>>4) address field.
-                        umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
-                                        (kb != w.kb_begin || k != 0) ? 1u : 0u);
+                        if (kTf32) {
+                            umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
+                                             (kb != w.kb_begin || k != 0) ? 1u : 0u);
+                        } else {
+                            umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
+                                            (kb != w.kb_begin || k != 0) ? 1u : 0u);
+                        }
                     }
                     // Free the stage (in both CTAs) once these MMAs have read it.
                     const uint32_t empty = smem_u32(&bars->empty[stage]);
@@ -467,12 +478,15 @@ struct Tuning {
 };
 static Tuning g_tuning;
 
-template <int CG, int BLOCK_N>
+template <int CG, int BLOCK_N, bool kTf32 = false>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
                   int max_ctas, DeviceState& dev, cudaStream_t stream)
 {
     using Cfg = Config<CG, BLOCK_N>;
-    auto kernel = gemm_kernel<CG, BLOCK_N>;
+    auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32>;
+    constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
+    constexpr CUtensorMapDataType kOperandType = kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    constexpr uint32_t kOperandBytes = kTf32 ? 4 : 2;
 
     static std::once_flag attr_once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
@@ -490,7 +504,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     p.K = K;
     p.tiles_m = (M + Cfg::kUmmaM - 1) / Cfg::kUmmaM;
     p.tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
-    p.num_kb = (K + kBlockK - 1) / kBlockK;
+    p.num_kb = (K + kElemsK - 1) / kElemsK;
     if (split_k > p.num_kb) {
         split_k = p.num_kb;
     }
@@ -507,11 +521,11 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     p.experiment = (uint32_t)tune.experiment;
 
     CUtensorMap tmap_a, tmap_b, tmap_c;
-    int rc = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, M, K, kBlockM, kBlockK);
+    int rc = make_tmap_2d(&tmap_a, kOperandType, kOperandBytes, A, M, K, kBlockM, kElemsK);
     if (rc) {
         return rc;
     }
-    rc = make_tmap_2d(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, N, K, Cfg::kBRows, kBlockK);
+    rc = make_tmap_2d(&tmap_b, kOperandType, kOperandBytes, B, N, K, Cfg::kBRows, kElemsK);
     if (rc) {
         return rc;
     }
@@ -565,9 +579,9 @@ static bool aligned16(const void* p)
 }
 
 static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int block_n,
-                    int cta_group, int split_k, int max_ctas, cudaStream_t stream)
+                    int cta_group, int split_k, int max_ctas, cudaStream_t stream, bool tf32 = false)
 {
-    if (!spork_gemm_sm100_supports(M, N, K)) {
+    if (tf32 ? (K % 4 != 0) : !spork_gemm_sm100_supports(M, N, K)) {
         return SPORK_ERR_UNSUPPORTED_SHAPE;
     }
     if (M == 0 || N == 0) {
@@ -594,6 +608,17 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
 #define SPORK_GEMM_CASE(CG_, BN_)                                                               \
     if (cta_group == CG_ && block_n == BN_) {                                                   \
         return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);                  \
+    }
+    if (tf32) {
+        if (cta_group != 2) {
+            return SPORK_ERR_BAD_ARGUMENT;
+        }
+        switch (block_n) {
+        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+        default: return SPORK_ERR_BAD_ARGUMENT;
+        }
     }
     SPORK_GEMM_CASE(1, 64)
     SPORK_GEMM_CASE(1, 128)
@@ -869,6 +894,20 @@ extern "C" int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, co
 {
     return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, cta_group, split_k, max_ctas,
                                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
+                                        int variant, int split_k, void* stream)
+{
+    int block_n = variant;
+    if (variant == 0) {
+        block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
+    }
+    if (block_n != 64 && block_n != 128 && block_n != 256) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, 2, split_k, 0, static_cast<cudaStream_t>(stream),
+                                       true);
 }
 
 extern "C" int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
