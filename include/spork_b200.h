@@ -112,8 +112,11 @@ int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 int spork_gemm_sm100_status(void* stream, uint32_t* detail);
 
 /* Host-buffer convenience (the htod_f32_* pattern of tk_4090_fwd.hpp:7): copies
- * A and B to the device, runs the GEMM, copies C back and synchronises.  Device
- * staging buffers are allocated on first use and kept. */
+ * A and B to the device, runs the GEMM, copies C back and synchronises.  A and C
+ * move in row chunks on separate copy-in / compute / copy-out streams so that
+ * both directions of the host link and the GEMM overlap (pass pinned host
+ * memory for that; pageable memory works, serialised).  Device staging buffers,
+ * streams and events are created on first use and kept. */
 int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* hA, const void* hB, float* hC);
 
 /* ---- Harness kernels (gemm/gemm_test.cu) --------------------------------- */
@@ -152,6 +155,10 @@ int spork_compare_f32(const float* d_a, const float* d_b, uint32_t rows, uint32_
 int spork_attn_sm100_supports(int BH, int S, int D);
 int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
                              void* stream);
+/* Same with bfloat16 q, k, v, o: the element type of the reference's HostAttnArgs
+ * (matrix_util.hpp:40-45) and of launch_tk_4090_fwd_kernel's output. */
+int spork_attn_sm100_fwd_bf16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
+                              void* stream);
 
 /* Reference-shaped FFI entry (tk_4090_fwd.hpp:7, called from
  * torch_attn.py:40-57): HOST fp32 (N, d) arrays, one head, scale 1/sqrt(d). */

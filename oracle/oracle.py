@@ -70,6 +70,12 @@ def lib() -> ctypes.CDLL:
         L.spork_oracle_ratio_compare.argtypes = [f32p, f32p, ctypes.c_uint32, ctypes.c_uint32]
         L.spork_oracle_attn_f16.restype = ctypes.c_int
         L.spork_oracle_attn_f16.argtypes = [ctypes.c_int] * 3 + [u16p, u16p, u16p, u16p, f32p, ctypes.c_float]
+        L.spork_oracle_attn_bf16.restype = ctypes.c_int
+        L.spork_oracle_attn_bf16.argtypes = [ctypes.c_int] * 3 + [u16p, u16p, u16p, u16p, f32p, ctypes.c_float]
+        L.spork_oracle_float_to_bf16.restype = ctypes.c_uint16
+        L.spork_oracle_float_to_bf16.argtypes = [ctypes.c_float]
+        L.spork_oracle_bf16_to_float.restype = ctypes.c_float
+        L.spork_oracle_bf16_to_float.argtypes = [ctypes.c_uint16]
         L.spork_oracle_num_threads.restype = ctypes.c_int
         L.spork_oracle_set_threads.argtypes = [ctypes.c_int]
         L.spork_oracle_set_threads.restype = None
@@ -201,3 +207,22 @@ def attn_f16(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float | None = 
     if rc:
         raise RuntimeError(f"oracle attention failed: {rc}")
     return o16.view(np.float16), o32
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    """uint16 bfloat16 bit patterns -> fp32 values."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def attn_bf16(q_bits: np.ndarray, k_bits: np.ndarray, v_bits: np.ndarray, scale: float | None = None):
+    """Attention on bfloat16 inputs given as uint16 bit patterns (BH, S, D); returns (o_bf16_bits, o_fp32)."""
+    Q, Kb, V = (np.ascontiguousarray(x, dtype=np.uint16) for x in (q_bits, k_bits, v_bits))
+    BH, S, D = Q.shape
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(D))
+    o16 = np.zeros((BH, S, D), dtype=np.uint16)
+    o32 = np.zeros((BH, S, D), dtype=np.float32)
+    rc = lib().spork_oracle_attn_bf16(BH, S, D, _u16(Q), _u16(Kb), _u16(V), _u16(o16), _f32(o32), scale)
+    if rc:
+        raise RuntimeError(f"oracle attention failed: {rc}")
+    return o16, o32

@@ -110,6 +110,29 @@ static inline uint16_t float_to_half_bits(float f)
 ORACLE_API float spork_oracle_half_to_float(uint16_t h) { return half_bits_to_float(h); }
 ORACLE_API uint16_t spork_oracle_float_to_half(float f) { return float_to_half_bits(f); }
 
+/* bfloat16 <-> fp32 (round to nearest even), the element type of the reference's attention interface. */
+static inline float bf16_bits_to_float(uint16_t h)
+{
+    const uint32_t bits = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+static inline uint16_t float_to_bf16_bits(float f)
+{
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    if ((x & 0x7FFFFFFFu) > 0x7F800000u) {
+        return (uint16_t)((x >> 16) | 0x40u); /* quiet NaN */
+    }
+    x += 0x7FFFu + ((x >> 16) & 1u);
+    return (uint16_t)(x >> 16);
+}
+
+ORACLE_API float spork_oracle_bf16_to_float(uint16_t h) { return bf16_bits_to_float(h); }
+ORACLE_API uint16_t spork_oracle_float_to_bf16(float f) { return float_to_bf16_bits(f); }
+
 /* ------------------------------------------------------------------------- */
 /* Position hash.  Follows gemm/gemm_test.cu:34-53 (the PCG3D hash of         */
 /* Jarzynski & Olano, folded to 64 bits the way the reference folds it).      */
@@ -409,8 +432,24 @@ ORACLE_API uint64_t spork_oracle_ratio_compare(const float* a_mat, const float* 
 /* Layout: [BH][S][D] row-major for q, k, v, o - each head is the reference's  */
 /* single (N, d) problem (matrix_util.hpp:40-45).                              */
 
+static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o16,
+                    float* o32, float scale, int bf16);
+
 ORACLE_API int spork_oracle_attn_f16(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                                      uint16_t* o16, float* o32, float scale)
+{
+    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 0);
+}
+
+/* Same with bfloat16 bit patterns in and out (the reference interface's element type). */
+ORACLE_API int spork_oracle_attn_bf16(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                      uint16_t* o16, float* o32, float scale)
+{
+    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 1);
+}
+
+static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o16,
+                    float* o32, float scale, int bf16)
 {
     if (BH < 0 || S <= 0 || D <= 0) {
         return 2;
@@ -440,13 +479,14 @@ ORACLE_API int spork_oracle_attn_f16(int BH, int S, int D, const uint16_t* q, co
             const size_t base = (size_t)h * S * D;
             if (h != cur_head) {
                 for (size_t e = 0; e < (size_t)S * D; ++e) {
-                    kf[e] = half_bits_to_float(k[base + e]);
-                    vf[e] = half_bits_to_float(v[base + e]);
+                    kf[e] = bf16 ? bf16_bits_to_float(k[base + e]) : half_bits_to_float(k[base + e]);
+                    vf[e] = bf16 ? bf16_bits_to_float(v[base + e]) : half_bits_to_float(v[base + e]);
                 }
                 cur_head = h;
             }
             for (int d = 0; d < D; ++d) {
-                qrow[d] = half_bits_to_float(q[base + (size_t)i * D + d]);
+                qrow[d] = bf16 ? bf16_bits_to_float(q[base + (size_t)i * D + d])
+                               : half_bits_to_float(q[base + (size_t)i * D + d]);
             }
             float row_max = -INFINITY;
             for (int j = 0; j < S; ++j) {
@@ -479,7 +519,7 @@ ORACLE_API int spork_oracle_attn_f16(int BH, int S, int D, const uint16_t* q, co
                     o32[base + (size_t)i * D + d] = orow[d];
                 }
                 if (o16) {
-                    o16[base + (size_t)i * D + d] = float_to_half_bits(orow[d]);
+                    o16[base + (size_t)i * D + d] = bf16 ? float_to_bf16_bits(orow[d]) : float_to_half_bits(orow[d]);
                 }
             }
         }

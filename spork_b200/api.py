@@ -86,6 +86,8 @@ def lib() -> ctypes.CDLL:
             L.spork_attn_sm100_supports.restype = i32
             L.spork_attn_sm100_fwd_f16.argtypes = [i32, i32, i32, vp, vp, vp, vp, ctypes.c_float, vp]
             L.spork_attn_sm100_fwd_f16.restype = i32
+            L.spork_attn_sm100_fwd_bf16.argtypes = [i32, i32, i32, vp, vp, vp, vp, ctypes.c_float, vp]
+            L.spork_attn_sm100_fwd_bf16.restype = i32
             L.htod_f32_attn_sm100_fwd.argtypes = [i32, i32, vp, vp, vp, vp]
             L.htod_f32_attn_sm100_fwd.restype = None
         L.spork_b200_version.restype = ctypes.c_char_p
@@ -254,7 +256,8 @@ def compare_f32(x, y, stream=None):
 
 
 def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None):
-    """o = softmax(q k^T scale) v per head; q, k, v are (BH, S, D) fp16 CUDA tensors."""
+    """o = softmax(q k^T scale) v per head; q, k, v are (BH, S, D) CUDA tensors, all fp16 or all bfloat16
+    (the reference interface's type)."""
     import torch
 
     BH, S, D = q.shape
@@ -262,9 +265,12 @@ def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None):
         o = torch.empty_like(q)
     if scale is None:
         scale = 1.0 / (D ** 0.5)
+    dt = q.dtype
+    if dt not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"q must be float16 or bfloat16, got {dt}")
+    fn = lib().spork_attn_sm100_fwd_f16 if dt == torch.float16 else lib().spork_attn_sm100_fwd_bf16
     with torch.cuda.device(q.device):
-        rc = lib().spork_attn_sm100_fwd_f16(BH, S, D, _dev_ptr(q, torch.float16, "q"), _dev_ptr(k, torch.float16, "k"),
-                                            _dev_ptr(v, torch.float16, "v"), _dev_ptr(o, torch.float16, "o"),
-                                            ctypes.c_float(scale), _stream_ptr(stream))
-    _check(rc, "spork_attn_sm100_fwd_f16")
+        rc = fn(BH, S, D, _dev_ptr(q, dt, "q"), _dev_ptr(k, dt, "k"), _dev_ptr(v, dt, "v"), _dev_ptr(o, dt, "o"),
+                ctypes.c_float(scale), _stream_ptr(stream))
+    _check(rc, "spork_attn_sm100_fwd")
     return o

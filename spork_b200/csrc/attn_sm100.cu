@@ -26,6 +26,7 @@
 // to -inf; rows past the end are computed on zero-filled queries and not stored.
 // Every wait is bounded (see ptx_sm100.cuh).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -69,7 +70,7 @@ struct Params {
     int q_pairs;        // ceil(S / 256): CTAs per head
     int kv_blocks;      // ceil(S / 128)
     float scale_log2e;  // scale * log2(e)
-    __half* o;
+    void* o;            // fp16 or bf16, [BH][S][D]
     uint32_t* status;
 };
 
@@ -91,8 +92,14 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
+// Two fp32 values rounded to a packed pair of 16-bit floats (low half first): fp16 or bf16.
+template <bool kBf16>
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
 {
+    if (kBf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
@@ -104,7 +111,8 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
     atomicCAS(p.status, 0u, 0x90000000u | (role << 24) | ((where & 0xFFu) << 16) | (blockIdx.x & 0xFFFFu));
 }
 
-template <int D>
+// kBf16: Q, K, V, P and O are bfloat16 (the reference interface's type, matrix_util.hpp:40-45) instead of fp16.
+template <int D, bool kBf16>
 __global__ void __launch_bounds__(kNumThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Params p)
@@ -195,8 +203,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false);
-            constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true);  // B = V is N-major
+            constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false, kBf16);
+            constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true, kBf16);  // B = V is N-major
             uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
             bool ok = true;
             auto advance = [&]() {
@@ -356,7 +364,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     const float p1 = ex2_approx(fmaf(__uint_as_float(r[half * 64 + 2 * i + 1]), sl2, neg_m));
                     l_blk0 += p0;
                     l_blk1 += p1;
-                    packed[i] = pack_half2(p0, p1);
+                    packed[i] = pack_half2<kBf16>(p0, p1);
                 }
                 tmem_st_32x32b_x32(tmem_s + half * 32, packed);
             }
@@ -392,7 +400,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             tcgen05_fence_after();
             const float inv_l = 1.0f / l_run;
             const int q_row = q_row0 + (int)w * kTileQ + (int)row;
-            __half* dst = p.o + ((size_t)head * p.S + (size_t)(q_row < p.S ? q_row : 0)) * D;
+            uint16_t* dst = static_cast<uint16_t*>(p.o) + ((size_t)head * p.S + (size_t)(q_row < p.S ? q_row : 0)) * D;
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
@@ -402,10 +410,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint4 v;
-                        v.x = pack_half2(__uint_as_float(r[8 * q4 + 0]) * inv_l, __uint_as_float(r[8 * q4 + 1]) * inv_l);
-                        v.y = pack_half2(__uint_as_float(r[8 * q4 + 2]) * inv_l, __uint_as_float(r[8 * q4 + 3]) * inv_l);
-                        v.z = pack_half2(__uint_as_float(r[8 * q4 + 4]) * inv_l, __uint_as_float(r[8 * q4 + 5]) * inv_l);
-                        v.w = pack_half2(__uint_as_float(r[8 * q4 + 6]) * inv_l, __uint_as_float(r[8 * q4 + 7]) * inv_l);
+                        v.x = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 0]) * inv_l, __uint_as_float(r[8 * q4 + 1]) * inv_l);
+                        v.y = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 2]) * inv_l, __uint_as_float(r[8 * q4 + 3]) * inv_l);
+                        v.z = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 4]) * inv_l, __uint_as_float(r[8 * q4 + 5]) * inv_l);
+                        v.w = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 6]) * inv_l, __uint_as_float(r[8 * q4 + 7]) * inv_l);
                         *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = v;
                     }
                 }
@@ -444,7 +452,7 @@ static EncodeTiledFn encode_tiled_fn()
 }
 
 // [BH][S][D] fp16 tensor, boxes of 128 rows x 64 columns (128 bytes, swizzled) of one head.
-static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int D)
+static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int D, bool bf16)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) {
@@ -454,18 +462,18 @@ static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int 
     const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)S * D * 2};
     const cuuint32_t box[3] = {64, 128, 1};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+    const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
                           elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
-template <int D>
+template <int D, bool kBf16>
 static int launch(int BH, int S, const void* q, const void* k, const void* v, void* o, float scale, DeviceState& dev,
                   cudaStream_t stream)
 {
     using Cfg = Config<D>;
-    auto kernel = attn_fwd_kernel<D>;
+    auto kernel = attn_fwd_kernel<D, kBf16>;
     static std::once_flag attr_once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(attr_once[dev.ordinal], [&] {
@@ -482,12 +490,12 @@ static int launch(int BH, int S, const void* q, const void* k, const void* v, vo
     p.q_pairs = (S + 2 * kTileQ - 1) / (2 * kTileQ);
     p.kv_blocks = (S + kTileKV - 1) / kTileKV;
     p.scale_log2e = scale * 1.4426950408889634f;
-    p.o = static_cast<__half*>(o);
+    p.o = o;
     p.status = dev.status_word;
     CUtensorMap tq, tk, tv;
     int rc;
-    if ((rc = make_tmap_bsd(&tq, q, BH, S, D)) != 0 || (rc = make_tmap_bsd(&tk, k, BH, S, D)) != 0 ||
-        (rc = make_tmap_bsd(&tv, v, BH, S, D)) != 0) {
+    if ((rc = make_tmap_bsd(&tq, q, BH, S, D, kBf16)) != 0 || (rc = make_tmap_bsd(&tk, k, BH, S, D, kBf16)) != 0 ||
+        (rc = make_tmap_bsd(&tv, v, BH, S, D, kBf16)) != 0) {
         return rc;
     }
     const long long ctas = (long long)BH * p.q_pairs;
@@ -520,8 +528,8 @@ extern "C" int spork_attn_sm100_supports(int BH, int S, int D)
     return (BH >= 0 && S >= 0 && (D == 64 || D == 128)) ? 1 : 0;
 }
 
-extern "C" int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,
-                                        float scale, void* stream)
+static int attn_dispatch(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
+                         void* stream, bool bf16)
 {
     if (!spork_attn_sm100_supports(BH, S, D)) {
         return SPORK_ERR_UNSUPPORTED_SHAPE;
@@ -539,10 +547,25 @@ extern "C" int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, con
         return rc;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    using namespace spork::attn_sm100;
     if (D == 64) {
-        return spork::attn_sm100::launch<64>(BH, S, q, k, v, o, scale, *dev, s);
+        return bf16 ? launch<64, true>(BH, S, q, k, v, o, scale, *dev, s)
+                    : launch<64, false>(BH, S, q, k, v, o, scale, *dev, s);
     }
-    return spork::attn_sm100::launch<128>(BH, S, q, k, v, o, scale, *dev, s);
+    return bf16 ? launch<128, true>(BH, S, q, k, v, o, scale, *dev, s)
+                : launch<128, false>(BH, S, q, k, v, o, scale, *dev, s);
+}
+
+extern "C" int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,
+                                        float scale, void* stream)
+{
+    return attn_dispatch(BH, S, D, q, k, v, o, scale, stream, false);
+}
+
+extern "C" int spork_attn_sm100_fwd_bf16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,
+                                         float scale, void* stream)
+{
+    return attn_dispatch(BH, S, D, q, k, v, o, scale, stream, true);
 }
 
 // Same signature and meaning as the reference's htod_f32_tk_4090_fwd

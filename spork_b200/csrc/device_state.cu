@@ -71,6 +71,27 @@ int ensure_staging(DeviceState& dev, int slot, size_t bytes)
     return 0;
 }
 
+int ensure_pipeline(DeviceState& dev)
+{
+    if (dev.pipe_ready) {
+        return 0;
+    }
+    for (auto& st : dev.pipe_streams) {
+        const cudaError_t e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            return (int)e;
+        }
+    }
+    for (auto& ev : dev.pipe_events) {
+        const cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e != cudaSuccess) {
+            return (int)e;
+        }
+    }
+    dev.pipe_ready = true;
+    return 0;
+}
+
 }  // namespace spork
 
 extern "C" int spork_gemm_sm100_status(void* stream, uint32_t* detail)

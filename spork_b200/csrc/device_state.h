@@ -26,11 +26,19 @@ struct DeviceState {
     // Staging buffers of the htod entry points (grown on demand, never shrunk).
     void* staging[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t staging_bytes[4] = {0, 0, 0, 0};
+    // Copy-in / compute / copy-out streams and hand-over events of the pipelined host-buffer GEMM.
+    static constexpr int kPipeChunks = 16;
+    bool pipe_ready = false;
+    cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t pipe_events[2 * kPipeChunks + 1] = {};
 };
 
 // State of the CURRENT device; creates it on first use.  Returns 0 or an error
 // code (SPORK_ERR_NO_SM100 when the device is not compute capability 10.x).
 int current_device_state(DeviceState** out);
+
+// Create the pipeline streams and events of `dev` on first use; returns 0 or a cudaError_t.
+int ensure_pipeline(DeviceState& dev);
 
 // Grow staging buffer `slot` of `dev` to at least `bytes`; returns 0 or a cudaError_t.
 int ensure_staging(DeviceState& dev, int slot, size_t bytes);

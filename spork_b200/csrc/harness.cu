@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/spork_b200.h"
 #include "device_state.h"
@@ -271,25 +272,79 @@ extern "C" int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, 
         (rc = spork::ensure_staging(*dev, 2, c_bytes)) != 0) {
         return rc;
     }
-    cudaStream_t s = cudaStreamPerThread;
-    cudaError_t e = cudaSuccess;
-    if (K != 0) {
-        e = cudaMemcpyAsync(dev->staging[0], hA, a_bytes, cudaMemcpyHostToDevice, s);
+    if (K == 0) {
+        memset(hC, 0, c_bytes);
+        return 0;
+    }
+    if ((rc = spork::ensure_pipeline(*dev)) != 0) {
+        return rc;
+    }
+    // Three streams: copy-in, compute, copy-out.  A and C move in row chunks so that the copy-in of chunk
+    // i+1, the GEMM of chunk i and the copy-out of chunk i-1 overlap (both directions of the host link are
+    // busy at once); B goes first, whole.  With pageable host memory the copies serialise but stay correct.
+    cudaStream_t s_in = dev->pipe_streams[0], s_comp = dev->pipe_streams[1], s_out = dev->pipe_streams[2];
+    constexpr int kMaxChunks = spork::DeviceState::kPipeChunks;
+    uint32_t chunk_rows = (M + 7) / 8;
+    chunk_rows = (chunk_rows + 255u) / 256u * 256u;  // whole output tiles per chunk
+    uint32_t chunks = (M + chunk_rows - 1) / chunk_rows;
+    if (chunks > (uint32_t)kMaxChunks) {
+        chunks = kMaxChunks;
+        chunk_rows = ((M + chunks - 1) / chunks + 255u) / 256u * 256u;
+        chunks = (M + chunk_rows - 1) / chunk_rows;
+    }
+    const char* a_host = static_cast<const char*>(hA);
+    char* a_dev = static_cast<char*>(dev->staging[0]);
+    float* c_dev = static_cast<float*>(dev->staging[2]);
+    cudaEvent_t* ev = dev->pipe_events;  // [0] B ready, [1 + i] A chunk i ready, [1 + kMaxChunks + i] C chunk i ready
+    cudaError_t e = cudaMemcpyAsync(dev->staging[1], hB, b_bytes, cudaMemcpyHostToDevice, s_in);
+    if (e == cudaSuccess) {
+        e = cudaEventRecord(ev[0], s_in);
+    }
+    if (e == cudaSuccess) {
+        e = cudaStreamWaitEvent(s_comp, ev[0], 0);
+    }
+    for (uint32_t i = 0; i < chunks && e == cudaSuccess; ++i) {
+        const uint32_t m0 = i * chunk_rows;
+        const uint32_t rows = M - m0 < chunk_rows ? M - m0 : chunk_rows;
+        const size_t a_off = size_t(m0) * K * 2;
+        e = cudaMemcpyAsync(a_dev + a_off, a_host + a_off, size_t(rows) * K * 2, cudaMemcpyHostToDevice, s_in);
         if (e == cudaSuccess) {
-            e = cudaMemcpyAsync(dev->staging[1], hB, b_bytes, cudaMemcpyHostToDevice, s);
+            e = cudaEventRecord(ev[1 + i], s_in);
+        }
+        if (e == cudaSuccess) {
+            e = cudaStreamWaitEvent(s_comp, ev[1 + i], 0);
         }
         if (e != cudaSuccess) {
-            return (int)e;
+            break;
+        }
+        rc = spork_gemm_sm100_f16f32(rows, N, K, a_dev + a_off, dev->staging[1], c_dev + size_t(m0) * N, 0, s_comp);
+        if (rc) {
+            break;
+        }
+        e = cudaEventRecord(ev[1 + kMaxChunks + i], s_comp);
+        if (e == cudaSuccess) {
+            e = cudaStreamWaitEvent(s_out, ev[1 + kMaxChunks + i], 0);
+        }
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(hC + size_t(m0) * N, c_dev + size_t(m0) * N, size_t(rows) * N * 4,
+                                cudaMemcpyDeviceToHost, s_out);
         }
     }
-    rc = spork_gemm_sm100_f16f32(M, N, K, dev->staging[0], dev->staging[1], static_cast<float*>(dev->staging[2]), 0,
-                                 s);
+    // Drain all three streams whatever happened, so that the staging buffers are idle on return.
+    const cudaError_t e_in = cudaStreamSynchronize(s_in);
+    const cudaError_t e_out = cudaStreamSynchronize(s_out);
+    const int status = spork_gemm_sm100_status(s_comp, nullptr);
     if (rc) {
         return rc;
     }
-    e = cudaMemcpyAsync(hC, dev->staging[2], c_bytes, cudaMemcpyDeviceToHost, s);
     if (e != cudaSuccess) {
         return (int)e;
     }
-    return spork_gemm_sm100_status(s, nullptr);
+    if (e_in != cudaSuccess) {
+        return (int)e_in;
+    }
+    if (e_out != cudaSuccess) {
+        return (int)e_out;
+    }
+    return status;
 }

@@ -376,11 +376,13 @@ __device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr, 
 
 // Instruction descriptor for kind::f16: fp16 A and B, fp32 accumulator.
 // a_mn_major / b_mn_major select the operand's contiguous direction.
+// `bf16` selects bfloat16 operands instead of fp16 (same instruction kind).
 __host__ __device__ constexpr uint32_t umma_idesc_f16_f32(uint32_t m, uint32_t n, bool a_mn_major = false,
-                                                          bool b_mn_major = false)
+                                                          bool b_mn_major = false, bool bf16 = false)
 {
     return (1u << 4)                          // accumulator format: fp32
-           | (0u << 7) | (0u << 10)           // A, B format: fp16
+           | ((bf16 ? 1u : 0u) << 7)          // A format: 0 = fp16, 1 = bf16
+           | ((bf16 ? 1u : 0u) << 10)         // B format
            | (a_mn_major ? (1u << 15) : 0u)   //
            | (b_mn_major ? (1u << 16) : 0u)   //
            | ((n >> 3) << 17)                 // N / 8

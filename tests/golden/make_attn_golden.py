@@ -49,6 +49,14 @@ def main():
                             q=q16.numpy(), k=k16.numpy(), v=v16.numpy(),
                             o=o.numpy().astype(np.float32), o_scale1=o_scale1.numpy().astype(np.float32))
         print(name, "written", o.shape, float(o.abs().max()))
+    # the reference interface's own element type and testbed size (attn_main.hpp:2-3): bfloat16, N=256, d=64
+    q, k, v = (make_rand(256, 64, s) for s in (101, 237, 280))
+    qb, kb, vb = (t.to(torch.bfloat16) for t in (q, k, v))
+    o = simple_attn(qb.float(), kb.float(), vb.float())
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
+    np.savez_compressed(os.path.join(HERE, "attn_simple_n256_d64_bf16.npz"), q_bits=bits(qb), k_bits=bits(kb),
+                        v_bits=bits(vb), o=o.numpy().astype(np.float32))
+    print("n256_d64_bf16 written", o.shape)
 
 
 if __name__ == "__main__":

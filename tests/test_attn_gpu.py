@@ -79,6 +79,45 @@ def test_golden_vectors_of_the_reference_math(sp, cuda, name):
     assert ok, f"max abs error {worst} (scale = 1)"
 
 
+# bfloat16 keeps 8 mantissa bits: P and O are rounded with a relative step of 2^-8
+ATOL_BF16 = 8e-3
+RTOL_BF16 = 2e-2
+
+
+def _bits(t):
+    import torch
+
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("BH,S,D", [(2, 256, 64), (2, 384, 128), (1, 200, 128), (3, 129, 64)])
+def test_bfloat16_variant_matches_oracle(sp, orc, cuda, BH, S, D):
+    """The reference interface's element type (HostAttnArgs holds __nv_bfloat16, matrix_util.hpp:40-45)."""
+    import torch
+
+    g = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn((BH, S, D), generator=g).to(torch.bfloat16).to(cuda) for _ in range(3))
+    o = sp.attn_fwd(q, k, v)
+    sp.status()
+    assert o.dtype == torch.bfloat16
+    _, ref = orc.attn_bf16(_bits(q), _bits(k), _bits(v))
+    got = o.float().cpu().numpy()
+    assert not (np.abs(got - ref) > ATOL_BF16 + RTOL_BF16 * np.abs(ref)).any(), float(np.abs(got - ref).max())
+
+
+def test_bfloat16_golden_vector_of_the_reference_math(sp, cuda):
+    """bfloat16 inputs at the reference's testbed size (attn_main.hpp:2-3) through its simple_attn."""
+    import torch
+
+    g = np.load(os.path.join(GOLDEN, "attn_simple_n256_d64_bf16.npz"))
+    q, k, v = (torch.from_numpy(g[n].view(np.int16)).view(torch.bfloat16).to(cuda)[None].contiguous()
+               for n in ("q_bits", "k_bits", "v_bits"))
+    o = sp.attn_fwd(q, k, v)
+    sp.status()
+    got = o[0].float().cpu().numpy()
+    assert not (np.abs(got - g["o"]) > ATOL_BF16 + RTOL_BF16 * np.abs(g["o"])).any()
+
+
 def test_softmax_properties_at_larger_sizes(sp, orc, cuda):
     """Sizes the CPU oracle cannot cover in full: (i) V = ones gives O = 1 exactly up to fp16 rounding of P's
     row sums; (ii) attention is invariant to a permutation of the keys/values; (iii) sampled heads against

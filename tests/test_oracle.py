@@ -185,6 +185,14 @@ def test_attention_oracle_matches_reference_math(orc, name):
     assert np.abs(o32_s1[0] - g["o_scale1"]).max() <= 2e-6 * max(1.0, float(np.abs(g["o_scale1"]).max()))
 
 
+def test_attention_oracle_bfloat16_matches_reference_math(orc):
+    g = np.load(os.path.join(GOLDEN, "attn_simple_n256_d64_bf16.npz"))
+    o16, o32 = orc.attn_bf16(g["q_bits"][None], g["k_bits"][None], g["v_bits"][None])
+    assert np.abs(o32[0] - g["o"]).max() <= 2e-6 * max(1.0, float(np.abs(g["o"]).max()))
+    # the rounded output is the nearest bfloat16 of the fp32 result
+    assert np.abs(orc.bf16_bits_to_f32(o16[0]) - o32[0]).max() <= 2.0 ** -8 * float(np.abs(o32).max())
+
+
 def test_attention_oracle_matches_torch_sdpa(orc):
     import torch
 
