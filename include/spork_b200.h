@@ -69,7 +69,12 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
  *   split_k   >= 1: K is cut into split_k ranges whose partial products are
  *             added into C with TMA reduce-add (C is zeroed first); the
  *             counterpart of gemm_sm90_k_mode::split_k_outer
- *             (gemm/gemm_sm90.h:8, gemm/gemm_sm90.cu:1096-1114)
+ *             (gemm/gemm_sm90.h:8, gemm/gemm_sm90.cu:1096-1114).
+ *             -1: stream-K, the counterpart of gemm_sm90_k_mode::stream_k_*
+ *             (gemm/gemm_sm90.h:10-11, gemm/gemm_sm90.cu:1004-1094): whole
+ *             waves of tiles run one tile per CTA pair, the K blocks of the
+ *             last partial wave are dealt out evenly over all CTA pairs and
+ *             reduce-added into their (zeroed) tiles
  *   max_ctas  0 = one CTA per SM, else an upper bound on the grid. */
 int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                int block_n, int cta_group, int split_k, int max_ctas, void* stream);

@@ -91,6 +91,10 @@ struct Params {
     uint32_t group_m;            // raster: m-tiles per group
     uint32_t l2_hints;           // bit 0: A loads evict_last, bit 1: B loads evict_last, bit 2: B loads evict_first
     uint32_t backoff_ns;         // sleep between polls of the long (epilogue / producer) waits; 0 = spin
+    // stream-K: the last `sk_tiles` tiles (raster order) are cut along K into one contiguous share of
+    // K blocks per CTA group and reduce-added into a zeroed C; the first `dp_tiles` run whole.
+    uint32_t dp_tiles, sk_tiles;
+    uint32_t sk_share, sk_extra; // group g owns sk_share (+1 if g < sk_extra) K blocks of the stream-K part
     uint32_t experiment;         // diagnostics only, results undefined: bit 0 = epilogue drops its stores,
                                  // bit 1 = producer stops issuing loads once the ring has been filled once,
                                  // bit 2 = epilogue stores straight from registers (no shared-memory staging)
@@ -109,16 +113,13 @@ struct Barriers {
 
 struct WorkItem {
     uint32_t m_tile, n_tile, kb_begin, kb_end, split;
+    bool reduce;  // the partial tile is added into C instead of stored
 };
 
 // Grouped raster (the superblock idea of gemm/gemm_sm90.cu:318-345): work items
 // that run at the same time cover kGroupM m-tiles by a run of n-tiles.
-__device__ __forceinline__ WorkItem decode_item(const Params& p, uint32_t item)
+__device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkItem& w)
 {
-    WorkItem w;
-    const uint32_t tiles = p.tiles_m * p.tiles_n;
-    const uint32_t split = item / tiles;
-    const uint32_t t = item % tiles;
     const uint32_t group_size = p.group_m * p.tiles_n;
     const uint32_t g = t / group_size;
     const uint32_t first_m = g * p.group_m;
@@ -126,10 +127,58 @@ __device__ __forceinline__ WorkItem decode_item(const Params& p, uint32_t item)
     const uint32_t r = t % group_size;
     w.m_tile = first_m + r % gm;
     w.n_tile = r / gm;
-    w.split = split;
-    w.kb_begin = split * p.kb_per_split;
-    const uint32_t e = w.kb_begin + p.kb_per_split;
-    w.kb_end = e < p.num_kb ? e : p.num_kb;
+}
+
+// Work of CTA group `g` of `G`.  Without stream-K: items g, g+G, ... of the (split, tile) list.  With
+// stream-K: first the whole tiles g, g+G, ... < dp_tiles, then this group's share of the K blocks of the
+// remaining tiles, which touches one or a few consecutive tiles.
+__device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
+{
+    if (p.sk_tiles == 0) {
+        const uint32_t items = p.tiles_m * p.tiles_n * p.split_k;
+        return items > g ? (items - g - 1) / G + 1 : 0;
+    }
+    const uint32_t n1 = p.dp_tiles / G;  // dp_tiles is a multiple of G
+    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
+    if (cnt == 0) {
+        return n1;
+    }
+    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
+    return n1 + ((u0 + cnt - 1) / p.num_kb - u0 / p.num_kb + 1);
+}
+
+__device__ __forceinline__ WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i)
+{
+    WorkItem w;
+    if (p.sk_tiles == 0) {
+        const uint32_t item = g + i * G;
+        const uint32_t tiles = p.tiles_m * p.tiles_n;
+        w.split = item / tiles;
+        decode_tile(p, item % tiles, w);
+        w.kb_begin = w.split * p.kb_per_split;
+        const uint32_t e = w.kb_begin + p.kb_per_split;
+        w.kb_end = e < p.num_kb ? e : p.num_kb;
+        w.reduce = p.split_k > 1;
+        return w;
+    }
+    w.split = 0;
+    const uint32_t n1 = p.dp_tiles / G;
+    if (i < n1) {
+        decode_tile(p, g + i * G, w);
+        w.kb_begin = 0;
+        w.kb_end = p.num_kb;
+        w.reduce = false;
+        return w;
+    }
+    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
+    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
+    const uint32_t rel = u0 / p.num_kb + (i - n1);   // tile index inside the stream-K part
+    const uint32_t t0 = rel * p.num_kb;              // its first K-block unit
+    decode_tile(p, p.dp_tiles + rel, w);
+    w.kb_begin = u0 > t0 ? u0 - t0 : 0;
+    const uint32_t u1 = u0 + cnt;
+    w.kb_end = u1 < t0 + p.num_kb ? u1 - t0 : p.num_kb;
+    w.reduce = true;
     return w;
 }
 
@@ -197,7 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
-    const uint32_t num_items = p.tiles_m * p.tiles_n * p.split_k;
+    const uint32_t num_items = group_item_count(p, group_id, num_groups);  // this CTA group's work items
     constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;  // elements along K per stage
 
     if (warp == 0) {
@@ -208,8 +257,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint64_t pol_a = (p.l2_hints & 1u) ? l2_policy_evict_last() : l2_policy_evict_normal();
             const uint64_t pol_b = (p.l2_hints & 2u) ? l2_policy_evict_last()
                                    : (p.l2_hints & 4u) ? l2_policy_evict_first() : l2_policy_evict_normal();
-            for (uint32_t item = group_id; item < num_items && ok; item += num_groups) {
-                const WorkItem w = decode_item(p, item);
+            for (uint32_t item = 0; item < num_items && ok; ++item) {
+                const WorkItem w = group_item(p, group_id, num_groups, item);
                 const int32_t a_row = (int32_t)(w.m_tile * Cfg::kUmmaM + cta_rank * kBlockM);
                 const int32_t b_row = (int32_t)(w.n_tile * BLOCK_N + cta_rank * Cfg::kBRows);
                 for (uint32_t kb = w.kb_begin; kb < w.kb_end; ++kb) {
@@ -254,8 +303,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
-            for (uint32_t item = group_id; item < num_items && ok; item += num_groups, ++local) {
-                const WorkItem w = decode_item(p, item);
+            for (uint32_t item = 0; item < num_items && ok; ++item, ++local) {
+                const WorkItem w = group_item(p, group_id, num_groups, item);
                 const uint32_t buf = local & 1u;
                 const uint32_t acc_phase = (local >> 1) & 1u;
                 if (!mbar_wait<CG == 2>(smem_u32(&bars->tmem_empty[buf]), acc_phase ^ 1u, abort_flag)) {
@@ -316,8 +365,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t local = 0;
         uint32_t slab_sel = 0;
         bool ok = true;
-        for (uint32_t item = group_id; item < num_items && ok; item += num_groups, ++local) {
-            const WorkItem w = decode_item(p, item);
+        for (uint32_t item = 0; item < num_items && ok; ++item, ++local) {
+            const WorkItem w = group_item(p, group_id, num_groups, item);
             const uint32_t buf = local & 1u;
             const uint32_t acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase, abort_flag, p.backoff_ns)) {
@@ -375,7 +424,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (lane == 0) {
                         if (kWorkspace) {
                             tma_store_3d(&tmap_c, slab, (int32_t)col, (int32_t)row0, (int32_t)w.split);
-                        } else if (p.split_k > 1) {
+                        } else if (w.reduce) {
                             tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
                         } else {
                             tma_store_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
@@ -389,7 +438,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             if (col + j < p.N) {
-                                if (p.split_k > 1) {
+                                if (w.reduce) {
                                     atomicAdd(dst + j, __uint_as_float(r[j]));
                                 } else {
                                     dst[j] = __uint_as_float(r[j]);
@@ -426,6 +475,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc<CG>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Zeroes the output tiles that stream-K accumulates into (tiles [first_tile, first_tile + count) of the
+// raster; one block per tile).
+template <int TILE_M, int TILE_N>
+__global__ void __launch_bounds__(256) zero_tiles_kernel(const Params p, uint32_t first_tile)
+{
+    WorkItem w;
+    decode_tile(p, first_tile + blockIdx.x, w);
+    const uint32_t m0 = w.m_tile * TILE_M, n0 = w.n_tile * TILE_N;
+    for (uint32_t i = threadIdx.x; i < (uint32_t)(TILE_M * TILE_N); i += blockDim.x) {
+        const uint32_t m = m0 + i / TILE_N, n = n0 + i % TILE_N;
+        if (m < p.M && n < p.N) {
+            p.C[(size_t)m * p.N + n] = 0.0f;
+        }
     }
 }
 
@@ -480,7 +545,7 @@ static Tuning g_tuning;
 
 template <int CG, int BLOCK_N, bool kTf32 = false>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
-                  int max_ctas, DeviceState& dev, cudaStream_t stream)
+                  int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false)
 {
     using Cfg = Config<CG, BLOCK_N>;
     auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32>;
@@ -553,7 +618,20 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     if (groups == 0) {
         groups = 1;
     }
-    if (items < groups) {
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    if (stream_k && p.split_k == 1 && tiles % groups != 0) {
+        // whole waves run tile by tile; the K blocks of the last partial wave are dealt out evenly
+        p.dp_tiles = tiles / groups * groups;
+        p.sk_tiles = tiles - p.dp_tiles;
+        const uint64_t units = (uint64_t)p.sk_tiles * p.num_kb;
+        p.sk_share = (uint32_t)(units / groups);
+        p.sk_extra = (uint32_t)(units % groups);
+        zero_tiles_kernel<Cfg::kUmmaM, BLOCK_N><<<p.sk_tiles, 256, 0, stream>>>(p, p.dp_tiles);
+        const cudaError_t ze = cudaGetLastError();
+        if (ze != cudaSuccess) {
+            return (int)ze;
+        }
+    } else if (items < groups) {
         groups = (uint32_t)items;
     }
 
@@ -593,7 +671,7 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
             return SPORK_ERR_BAD_ARGUMENT;
         }
     }
-    if (split_k < 1 || max_ctas < 0) {
+    if ((split_k < 1 && split_k != -1) || max_ctas < 0) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     if (K == 0) {
@@ -604,19 +682,20 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     if (rc) {
         return rc;
     }
-    const uint32_t sk = (uint32_t)split_k;
+    const bool stream_k = split_k == -1;
+    const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
 #define SPORK_GEMM_CASE(CG_, BN_)                                                               \
     if (cta_group == CG_ && block_n == BN_) {                                                   \
-        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);                  \
+        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);        \
     }
     if (tf32) {
         if (cta_group != 2) {
             return SPORK_ERR_BAD_ARGUMENT;
         }
         switch (block_n) {
-        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
-        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
-        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }

@@ -30,8 +30,9 @@ enum class AlgorithmCode {
     mine_sm_100_n128,
     mine_sm_100_n64,
     mine_sm_100_split_k,
+    mine_sm_100_stream_k,
 };
-constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_split_k);
+constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_stream_k);
 
 inline uint32_t algorithm_code_bit(AlgorithmCode code) { return 1u << static_cast<uint32_t>(code); }
 
@@ -44,6 +45,7 @@ inline const char* algorithm_name(AlgorithmCode code)
     case AlgorithmCode::mine_sm_100_n128: return "mine_sm_100_n128";
     case AlgorithmCode::mine_sm_100_n64: return "mine_sm_100_n64";
     case AlgorithmCode::mine_sm_100_split_k: return "mine_sm_100 (split k)";
+    case AlgorithmCode::mine_sm_100_stream_k: return "mine_sm_100 (stream k)";
     }
     return "unknown";
 }
@@ -133,6 +135,9 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
                 break;
             case AlgorithmCode::mine_sm_100_split_k:
                 launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::split_k_outer, 4);
+                break;
+            case AlgorithmCode::mine_sm_100_stream_k:
+                launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::stream_k);
                 break;
             }
             CUDA_OK(cudaEventRecord(test_events[test_i + 1], stream));
@@ -234,6 +239,7 @@ int main(int argc, char** argv)
             if (K >= 4096) {
                 params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_split_k);
             }
+            params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_stream_k);
         }
         auto run = [&](TestDataCode a, TestDataCode b) {
             params.test_data_code_A = a;

@@ -153,6 +153,20 @@ def test_split_k_reduce_add(sp, orc, cuda, split_k):
         _check(sp, orc, a, b, c, K)
 
 
+@pytest.mark.parametrize("shape", [(1536, 2304, 8192), (512, 512, 4096), (16384, 64, 1024), (160, 480, 816),
+                                   (2048, 6000, 264), (300, 131, 2056), (256, 256, 64)])
+def test_stream_k(sp, orc, cuda, shape):
+    """split_k = -1: whole waves tile by tile, the K blocks of the last partial wave dealt out over all CTA
+    pairs (the reference's stream-K modes, gemm/gemm_sm90.cu:1004-1094)."""
+    M, N, K = shape
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    for cta_group, block_n, max_ctas in ((2, 256, 0), (1, 128, 0), (2, 64, 20)):
+        c = _poisoned(cuda, M, N)
+        sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=cta_group, split_k=-1, max_ctas=max_ctas)
+        sp.status()
+        _check(sp, orc, a, b, c, K)
+
+
 def test_n_not_multiple_of_four_uses_guarded_stores(sp, orc, cuda):
     for M, N, K in ((130, 67, 72), (256, 1, 64), (300, 131, 136)):
         a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
