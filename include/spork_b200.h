@@ -110,6 +110,23 @@ int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K, const voi
  * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
 int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);
 
+/* Host-only view of how a launch would be laid out (no CUDA call; usable without a
+ * GPU).  Arguments as for the _ex entry point, plus the SM count to plan for and
+ * tf32 (0/1).  out[10] = tiles_m, tiles_n, K blocks, splits, K blocks per split,
+ * CTA groups (CTAs / cta_group), whole-tile count, stream-K tile count, stream-K
+ * share per group, groups that get one extra block.  The reference computes the
+ * equivalent inside its kernel (gemm/gemm_sm90.cu:1004-1129). */
+int spork_gemm_sm100_plan(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k, int max_ctas,
+                          int sm_count, int tf32, uint32_t* out);
+
+/* The work items CTA group `group` would process, in order: 5 words per item
+ * (m_tile, n_tile, first K block, end K block, 1 if the partial tile is added
+ * into C).  Returns the item count (items beyond `capacity` are not written),
+ * or -1 on bad arguments. */
+int spork_gemm_sm100_plan_items(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k,
+                                int max_ctas, int sm_count, int tf32, uint32_t group, uint32_t* out,
+                                uint32_t capacity);
+
 /* Synchronises `stream`, then returns and clears the device status word of the
  * current device: 0, or SPORK_ERR_DEVICE_TIMEOUT if a kernel abandoned a
  * bounded wait (detail word through *detail when non-null).  Replaces the

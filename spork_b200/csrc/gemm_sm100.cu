@@ -118,7 +118,7 @@ struct WorkItem {
 
 // Grouped raster (the superblock idea of gemm/gemm_sm90.cu:318-345): work items
 // that run at the same time cover kGroupM m-tiles by a run of n-tiles.
-__device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkItem& w)
+__host__ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkItem& w)
 {
     const uint32_t group_size = p.group_m * p.tiles_n;
     const uint32_t g = t / group_size;
@@ -132,7 +132,7 @@ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkIte
 // Work of CTA group `g` of `G`.  Without stream-K: items g, g+G, ... of the (split, tile) list.  With
 // stream-K: first the whole tiles g, g+G, ... < dp_tiles, then this group's share of the K blocks of the
 // remaining tiles, which touches one or a few consecutive tiles.
-__device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
+__host__ __device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
 {
     if (p.sk_tiles == 0) {
         const uint32_t items = p.tiles_m * p.tiles_n * p.split_k;
@@ -147,7 +147,7 @@ __device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g
     return n1 + ((u0 + cnt - 1) / p.num_kb - u0 / p.num_kb + 1);
 }
 
-__device__ __forceinline__ WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i)
+__host__ __device__ __forceinline__ WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i)
 {
     WorkItem w;
     if (p.sk_tiles == 0) {
@@ -533,6 +533,52 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
+// Host-side launch plan: tile grid, K split, number of CTA groups and the stream-K partition.  Pure
+// arithmetic (no CUDA call), shared by the launch paths and by spork_gemm_sm100_plan.
+static void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m,
+                        uint32_t block_n, uint32_t cta_group, uint32_t elems_k, uint32_t split_k, bool stream_k,
+                        int max_ctas, int sm_count)
+{
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.tiles_m = (M + tile_m - 1) / tile_m;
+    p.tiles_n = (N + block_n - 1) / block_n;
+    p.num_kb = (K + elems_k - 1) / elems_k;
+    if (split_k > p.num_kb) {
+        split_k = p.num_kb;
+    }
+    if (split_k < 1) {
+        split_k = 1;
+    }
+    p.kb_per_split = (p.num_kb + split_k - 1) / split_k;
+    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
+    p.use_tma_store = (N % 4 == 0) ? 1u : 0u;
+    p.dp_tiles = 0;
+    p.sk_tiles = 0;
+    p.sk_share = 0;
+    p.sk_extra = 0;
+    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k;
+    groups = (uint32_t)(sm_count / (int)cta_group);
+    if (max_ctas > 0 && (uint32_t)max_ctas / cta_group < groups) {
+        groups = (uint32_t)max_ctas / cta_group;
+    }
+    if (groups == 0) {
+        groups = 1;
+    }
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    if (stream_k && p.split_k == 1 && tiles % groups != 0) {
+        // whole waves run tile by tile; the K blocks of the last partial wave are dealt out evenly
+        p.dp_tiles = tiles / groups * groups;
+        p.sk_tiles = tiles - p.dp_tiles;
+        const uint64_t units = (uint64_t)p.sk_tiles * p.num_kb;
+        p.sk_share = (uint32_t)(units / groups);
+        p.sk_extra = (uint32_t)(units % groups);
+    } else if (items < groups) {
+        groups = (uint32_t)items;
+    }
+}
+
 // Process-wide tuning knobs (spork_gemm_sm100_tune); the defaults are the measured best.
 struct Tuning {
     int stages = 0;       // 0 = as deep as shared memory allows
@@ -564,18 +610,8 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     }
 
     Params p{};
-    p.M = M;
-    p.N = N;
-    p.K = K;
-    p.tiles_m = (M + Cfg::kUmmaM - 1) / Cfg::kUmmaM;
-    p.tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
-    p.num_kb = (K + kElemsK - 1) / kElemsK;
-    if (split_k > p.num_kb) {
-        split_k = p.num_kb;
-    }
-    p.kb_per_split = (p.num_kb + split_k - 1) / split_k;
-    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
-    p.use_tma_store = (N % 4 == 0) ? 1u : 0u;
+    uint32_t groups = 1;
+    plan_launch(p, groups, M, N, K, Cfg::kUmmaM, BLOCK_N, CG, kElemsK, split_k, stream_k, max_ctas, dev.sm_count);
     p.C = C;
     p.status = dev.status_word;
     const Tuning tune = g_tuning;
@@ -610,29 +646,12 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
         }
     }
 
-    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k;
-    uint32_t groups = (uint32_t)(dev.sm_count / CG);
-    if (max_ctas > 0 && (uint32_t)(max_ctas / CG) < groups) {
-        groups = (uint32_t)(max_ctas / CG);
-    }
-    if (groups == 0) {
-        groups = 1;
-    }
-    const uint32_t tiles = p.tiles_m * p.tiles_n;
-    if (stream_k && p.split_k == 1 && tiles % groups != 0) {
-        // whole waves run tile by tile; the K blocks of the last partial wave are dealt out evenly
-        p.dp_tiles = tiles / groups * groups;
-        p.sk_tiles = tiles - p.dp_tiles;
-        const uint64_t units = (uint64_t)p.sk_tiles * p.num_kb;
-        p.sk_share = (uint32_t)(units / groups);
-        p.sk_extra = (uint32_t)(units % groups);
+    if (p.sk_tiles != 0) {
         zero_tiles_kernel<Cfg::kUmmaM, BLOCK_N><<<p.sk_tiles, 256, 0, stream>>>(p, p.dp_tiles);
         const cudaError_t ze = cudaGetLastError();
         if (ze != cudaSuccess) {
             return (int)ze;
         }
-    } else if (items < groups) {
-        groups = (uint32_t)items;
     }
 
     cudaLaunchConfig_t cfg{};
@@ -945,6 +964,59 @@ extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K
         return launch_static<128>(M, N, K, A, B, C, (uint32_t)split_k, dev, ordinal, stream);
     }
     return launch_static<256>(M, N, K, A, B, C, (uint32_t)split_k, dev, ordinal, stream);
+}
+
+// Geometry of a plan as a flat array (see the header for the order).
+static bool plan_from_args(spork::gemm_sm100::Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K,
+                           int block_n, int cta_group, int split_k, int max_ctas, int sm_count, int tf32)
+{
+    if ((block_n != 64 && block_n != 128 && block_n != 256) || (cta_group != 1 && cta_group != 2) ||
+        (split_k < 1 && split_k != -1) || max_ctas < 0 || sm_count < cta_group) {
+        return false;
+    }
+    spork::gemm_sm100::plan_launch(p, groups, M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n,
+                                   (uint32_t)cta_group, tf32 ? 32u : 64u, split_k == -1 ? 1u : (uint32_t)split_k,
+                                   split_k == -1, max_ctas, sm_count);
+    p.group_m = (uint32_t)spork::gemm_sm100::kGroupM;
+    return true;
+}
+
+extern "C" int spork_gemm_sm100_plan(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k,
+                                     int max_ctas, int sm_count, int tf32, uint32_t* out)
+{
+    spork::gemm_sm100::Params p{};
+    uint32_t groups = 0;
+    if (!out || !plan_from_args(p, groups, M, N, K, block_n, cta_group, split_k, max_ctas, sm_count, tf32)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    const uint32_t vals[10] = {p.tiles_m, p.tiles_n, p.num_kb, p.split_k, p.kb_per_split, groups,
+                               p.dp_tiles, p.sk_tiles, p.sk_share, p.sk_extra};
+    for (int i = 0; i < 10; ++i) {
+        out[i] = vals[i];
+    }
+    return 0;
+}
+
+extern "C" int spork_gemm_sm100_plan_items(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group,
+                                           int split_k, int max_ctas, int sm_count, int tf32, uint32_t group,
+                                           uint32_t* out, uint32_t capacity)
+{
+    spork::gemm_sm100::Params p{};
+    uint32_t groups = 0;
+    if (!plan_from_args(p, groups, M, N, K, block_n, cta_group, split_k, max_ctas, sm_count, tf32) ||
+        group >= groups) {
+        return -1;
+    }
+    const uint32_t count = (M == 0 || N == 0 || K == 0) ? 0u : spork::gemm_sm100::group_item_count(p, group, groups);
+    for (uint32_t i = 0; i < count && i < capacity; ++i) {
+        const spork::gemm_sm100::WorkItem w = spork::gemm_sm100::group_item(p, group, groups, i);
+        out[5 * i + 0] = w.m_tile;
+        out[5 * i + 1] = w.n_tile;
+        out[5 * i + 2] = w.kb_begin;
+        out[5 * i + 3] = w.kb_end;
+        out[5 * i + 4] = w.reduce ? 1u : 0u;
+    }
+    return (int)count;
 }
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)

@@ -1,0 +1,92 @@
+"""CPU tests of the GEMM's host-side launch plan (tile grid, K splits, stream-K partition, raster): the same
+C++ functions the kernel runs are enumerated through the C ABI, no GPU involved."""
+import ctypes
+
+import pytest
+
+
+def _plan(L, M, N, K, bn, cg, sk, max_ctas=0, sms=148, tf32=0):
+    out = (ctypes.c_uint32 * 10)()
+    rc = L.spork_gemm_sm100_plan(M, N, K, bn, cg, sk, max_ctas, sms, tf32, out)
+    assert rc == 0
+    keys = ["tiles_m", "tiles_n", "num_kb", "split_k", "kb_per_split", "groups", "dp_tiles", "sk_tiles", "sk_share",
+            "sk_extra"]
+    return dict(zip(keys, list(out)))
+
+
+def _items(L, M, N, K, bn, cg, sk, group, max_ctas=0, sms=148, tf32=0):
+    cap = 4096
+    buf = (ctypes.c_uint32 * (5 * cap))()
+    n = L.spork_gemm_sm100_plan_items(M, N, K, bn, cg, sk, max_ctas, sms, tf32, group, buf, cap)
+    assert 0 <= n <= cap
+    return [tuple(buf[5 * i:5 * i + 5]) for i in range(n)]
+
+
+@pytest.fixture(scope="module")
+def L(sp):
+    lib = sp.lib()
+    u32, i32 = ctypes.c_uint32, ctypes.c_int
+    lib.spork_gemm_sm100_plan.argtypes = [u32, u32, u32, i32, i32, i32, i32, i32, i32, ctypes.POINTER(u32)]
+    lib.spork_gemm_sm100_plan.restype = i32
+    lib.spork_gemm_sm100_plan_items.argtypes = [u32, u32, u32, i32, i32, i32, i32, i32, i32, u32, ctypes.POINTER(u32), u32]
+    lib.spork_gemm_sm100_plan_items.restype = i32
+    return lib
+
+
+def test_headline_plan(L):
+    p = _plan(L, 8192, 8192, 8192, 256, 2, 1)
+    assert (p["tiles_m"], p["tiles_n"], p["num_kb"], p["groups"]) == (32, 32, 128, 74)
+    assert p["split_k"] == 1 and p["sk_tiles"] == 0
+    p = _plan(L, 16384, 64, 8192, 64, 2, 1)
+    assert (p["tiles_m"], p["tiles_n"], p["groups"]) == (64, 1, 64)  # fewer tiles than CTA pairs
+    p = _plan(L, 8192, 8192, 8192, 256, 2, 1, tf32=1)
+    assert p["num_kb"] == 256  # 32 fp32 elements per 128-byte row
+
+
+def test_split_k_is_normalised(L):
+    p = _plan(L, 512, 512, 2048, 128, 2, 1000)
+    assert p["num_kb"] == 32 and p["split_k"] == 32 and p["kb_per_split"] == 1
+    p = _plan(L, 512, 512, 2048, 128, 2, 3)
+    assert p["kb_per_split"] == 11 and p["split_k"] == 3  # 11 + 11 + 10, no empty split
+    assert L.spork_gemm_sm100_plan(1, 1, 8, 100, 2, 1, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001
+    assert L.spork_gemm_sm100_plan(1, 1, 8, 128, 2, 0, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001
+
+
+@pytest.mark.parametrize("shape,bn,cg,sk,max_ctas", [
+    ((8192, 8192, 8192), 256, 2, 1, 0), ((1536, 2304, 65536), 256, 2, -1, 0), ((16384, 64, 8192), 64, 2, -1, 0),
+    ((160, 480, 816), 128, 1, -1, 0), ((2048, 6000, 264), 64, 2, -1, 20), ((1000, 264, 136), 256, 2, 1, 0),
+    ((768, 768, 4096), 256, 1, 4, 0), ((300, 131, 2056), 128, 2, -1, 0), ((8192, 8192, 8192), 256, 2, -1, 0),
+    ((4096, 4096, 64), 128, 2, 3, 6),
+])
+def test_every_k_block_of_every_tile_is_covered_exactly_once(L, shape, bn, cg, sk, max_ctas):
+    M, N, K = shape
+    p = _plan(L, M, N, K, bn, cg, sk, max_ctas)
+    covered = {}
+    reduce_tiles = set()
+    for g in range(p["groups"]):
+        for (m, n, kb0, kb1, red) in _items(L, M, N, K, bn, cg, sk, g, max_ctas):
+            assert m < p["tiles_m"] and n < p["tiles_n"] and kb0 < kb1 <= p["num_kb"]
+            if red:
+                reduce_tiles.add((m, n))
+            for kb in range(kb0, kb1):
+                assert (m, n, kb) not in covered, "K block computed twice"
+                covered[(m, n, kb)] = (g, red)
+    assert len(covered) == p["tiles_m"] * p["tiles_n"] * p["num_kb"]
+    # a tile is either stored whole by one group or reduce-added by all of its contributors, never mixed
+    for (m, n, kb), (g, red) in covered.items():
+        assert bool(red) == ((m, n) in reduce_tiles)
+    if sk == 1:
+        assert not reduce_tiles
+    if p["sk_tiles"]:
+        assert len(reduce_tiles) == p["sk_tiles"]
+        loads = [sum(kb1 - kb0 for (_, _, kb0, kb1, red) in _items(L, M, N, K, bn, cg, sk, g, max_ctas) if red)
+                 for g in range(p["groups"])]
+        assert max(loads) - min(loads) <= 1  # the stream-K part is balanced to one K block
+
+
+def test_raster_keeps_concurrent_tiles_compact(L):
+    """Tiles that run in the same wave span 8 m-tiles and a short run of n-tiles (the superblock raster)."""
+    firsts = [_items(L, 8192, 8192, 8192, 256, 2, 1, g)[0][:2] for g in range(74)]
+    ms = {m for m, _ in firsts}
+    ns = {n for _, n in firsts}
+    assert ms == set(range(8)) and len(ns) <= 10
