@@ -329,6 +329,7 @@ def main():
         torch.cuda.synchronize()
     barrier()
     sp.status()
+    in_kernel_mhz = sp.last_clock_mhz()  # SM clock of the last timed launch, measured inside the kernel
     total_ms = events[0].elapsed_time(events[-1])
     launch_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -395,7 +396,10 @@ def main():
                 "peak_kind": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['bf16_tflops_sustained']})",
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "kernel": "spork::gemm_sm100::gemm_kernel<2,256>", "algorithmic_bytes": BYTES_PER_STEP,
-                "avg_launch_ms": avg_launch_ms, "min_launch_ms": min(launch_ms)}
+                "avg_launch_ms": avg_launch_ms, "min_launch_ms": min(launch_ms),
+                "sm_mhz_in_kernel": in_kernel_mhz,
+                "frac_of_peak_at_that_clock": (FLOPS_PER_STEP / (launch_ms[-1] * 1e-3) / 1e12) /
+                                              (148 * 8192 * in_kernel_mhz * 1e6 / 1e12) if in_kernel_mhz > 0 else None}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -412,7 +416,7 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic", "config": config_dict(world),
-            "clocks": clocks.summary(),
+            "clocks": dict(clocks.summary(), sm_mhz_in_kernel=in_kernel_mhz),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM,
                     "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
             "gpu_launches": args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,

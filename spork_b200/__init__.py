@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     compare_f32,
     gemm_baseline,
     init_test_data,
+    last_clock_mhz,
     lib,
     library_path,
     matmul_sm100,

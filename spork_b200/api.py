@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_f16f32_ex.restype = i32
         L.spork_gemm_sm100_f16f32_static.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
         L.spork_gemm_sm100_f16f32_static.restype = i32
+        L.spork_gemm_sm100_last_clock_mhz.argtypes = [vp, ctypes.POINTER(ctypes.c_double)]
+        L.spork_gemm_sm100_last_clock_mhz.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
         L.spork_gemm_sm100_tune.restype = i32
         L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]
@@ -175,6 +177,13 @@ def matmul_sm100_tf32(a, b, c=None, *, variant: int = 0, split_k: int = 1, strea
         rc = lib().spork_gemm_sm100_tf32f32(M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
     _check(rc, "spork_gemm_sm100_tf32f32")
     return c
+
+
+def last_clock_mhz(stream=None) -> float:
+    """SM clock the most recent GEMM launch on the current device ran at (measured inside the kernel)."""
+    mhz = ctypes.c_double(0.0)
+    _check(lib().spork_gemm_sm100_last_clock_mhz(_stream_ptr(stream), ctypes.byref(mhz)), "last_clock_mhz")
+    return float(mhz.value)
 
 
 def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0) -> None:

@@ -34,12 +34,13 @@ int current_device_state(DeviceState** out)
         if (e != cudaSuccess) {
             return (int)e;
         }
+        // 64 bytes: [0] status word, [16..48) clock probe of the last GEMM launch (see gemm_sm100.cu)
         uint32_t* word = nullptr;
-        e = cudaMalloc(&word, sizeof(uint32_t));
+        e = cudaMalloc(&word, 64);
         if (e != cudaSuccess) {
             return (int)e;
         }
-        e = cudaMemset(word, 0, sizeof(uint32_t));
+        e = cudaMemset(word, 0, 64);
         if (e != cudaSuccess) {
             cudaFree(word);
             return (int)e;

@@ -215,6 +215,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (staging_base + Cfg::kStagingBytes - smem_u32(smem_raw)));
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
+    // Clock probe: CTA 0 notes SM cycles and wall-clock nanoseconds at both ends of the launch; their
+    // ratio is the SM clock the kernel really ran at (the power cap moves it far below the nominal clock).
+    unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
+    if (!kWorkspace && blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
@@ -475,6 +482,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc<CG>(tmem_base, Cfg::kTmemCols);
+    }
+    if (!kWorkspace && blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[2] = (unsigned long long)clock64();
+        probe[3] = global_timer_ns();
     }
 }
 
@@ -1017,6 +1028,29 @@ extern "C" int spork_gemm_sm100_plan_items(uint32_t M, uint32_t N, uint32_t K, i
         out[5 * i + 4] = w.reduce ? 1u : 0u;
     }
     return (int)count;
+}
+
+extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
+{
+    spork::DeviceState* dev = nullptr;
+    const int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    if (!mhz) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long probe[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaMemcpyAsync(probe, dev->status_word + 4, sizeof(probe), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(s);
+    }
+    if (e != cudaSuccess) {
+        return (int)e;
+    }
+    *mhz = probe[3] > probe[1] ? double(probe[2] - probe[0]) / double(probe[3] - probe[1]) * 1e3 : 0.0;
+    return 0;
 }
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)

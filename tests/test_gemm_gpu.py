@@ -253,6 +253,15 @@ def test_non_default_stream_and_back_to_back_launches(sp, orc, cuda):
     _check(sp, orc, a, b, cs[0], K)
 
 
+def test_in_kernel_clock_probe(sp, orc, cuda):
+    M = N = K = 4096
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    sp.matmul_sm100(a, b)
+    sp.status()
+    mhz = sp.last_clock_mhz()
+    assert 300.0 < mhz < 2500.0, mhz  # a B200 runs between its idle clock and 1965 MHz
+
+
 def test_headline_size_properties(sp, orc, cuda):
     """8192^3 (the headline configuration): whole-matrix comparison against the CUDA-core comparison kernel,
     CPU-oracle check of sampled row blocks including both matrix edges, and linearity in A."""
