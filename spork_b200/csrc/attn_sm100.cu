@@ -62,7 +62,7 @@ struct Config {
     static constexpr int kStagesFit = (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes;
     static constexpr int kKvStages = kStagesFit > kMaxKvStages ? kMaxKvStages : kStagesFit;
     static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + kKvStages * kTileBytes + 1024;
-    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory limit");
 };
 
 struct Params {
@@ -213,27 +213,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     phase ^= 1u;
                 }
             };
+            // Descriptor low words: one per operand tile, advanced by compile-time constants per MMA
+            // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
+            // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
+            const uint32_t q_lo[2] = {desc_lo_kmajor(q_smem), desc_lo_kmajor(q_smem + Cfg::kTileBytes)};
             // S_w = Q_w K^T from the K tile in ring slot `st`
             auto issue_qk = [&](int w, uint32_t st) {
-                const uint32_t qa = q_smem + w * Cfg::kTileBytes;
-                const uint32_t kb = kv_smem + st * Cfg::kTileBytes;
+                const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t da = umma_desc_kmajor_sw128(qa + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
-                    const uint64_t db = umma_desc_kmajor_sw128(kb + (kk / 4) * Cfg::kAtomBytes) + 2u * (kk % 4);
-                    umma_f16_ss<1>(tmem_s0 + w * 128, da, db, idesc_qk, kk != 0 ? 1u : 0u);
+                    const uint32_t off = (uint32_t)((kk / 4) * (Cfg::kAtomBytes >> 4) + 2 * (kk % 4));
+                    umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo[w] + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
+                                     kk != 0 ? 1u : 0u);
                 }
             };
             // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
-            // B = the V tile in ring slot `st`
+            // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart)
             auto issue_pv = [&](int w, uint32_t st, bool accumulate) {
-                const uint32_t vb = kv_smem + st * Cfg::kTileBytes;
+                const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
 #pragma unroll
                 for (int kk = 0; kk < kTileKV / 16; ++kk) {
-                    // 16 keys = 16 rows of 128 bytes further down the V tile; d-halves are one atom apart
-                    const uint64_t db = umma_desc_mnmajor_sw128(vb + kk * 16 * 128, Cfg::kAtomBytes, 1024);
-                    umma_f16_ts<1>(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, db, idesc_pv,
-                                   (accumulate || kk != 0) ? 1u : 0u);
+                    umma_f16_ts_cta1(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
+                                     kDescHiSw128, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
                 }
             };
             do {

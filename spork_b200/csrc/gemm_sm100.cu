@@ -76,7 +76,7 @@ struct Config {
     static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;  // 128 / 256 / 512: powers of two
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStagingBytes + kBarrierBytes;
     static_assert(kStages >= 2, "ring too shallow");
-    static_assert(kSmemBytes <= kMaxSmem, "shared memory budget");
+    static_assert(kSmemBytes <= kMaxSmem, "shared memory limit");
     static_assert(kUmmaN % 16 == 0 && kUmmaN >= 16 && kUmmaN <= 256, "UMMA N");
 };
 

@@ -90,8 +90,8 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
     fill_garbage(d_c_baseline);
     matmul_baseline_f16(GPU_TensorsF16{params.M, params.N, params.K, d_a, d_bCol, d_c_baseline, 0, 1, 0}, stream);
 
-    // Signed data cancels, so the sign + ratio rule only judges the reference's non-negative fixtures;
-    // the normalised error max|err| / (max|A| max|B| K 2^-10) <= 1 judges everything.
+    // Signed data cancels, so the sign + ratio rule only applies to the reference's non-negative fixtures;
+    // the normalised error max|err| / (max|A| max|B| K 2^-10) <= 1 applies to everything.
     const bool ratio_rule = params.test_data_code_A != TestDataCode::uniform_pm1;
     auto max_abs = [](TestDataCode c) { return c == TestDataCode::tiled_numbers ? 6364.0 : (c == TestDataCode::random ? 1000.0 : 1.0); };
     const double denom = max_abs(params.test_data_code_A) * max_abs(params.test_data_code_B) * double(params.K) / 1024.0;

@@ -451,6 +451,54 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32_f32(uint32_t m, uint32_t 
     return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// The same two MMAs taking each 64-bit shared-memory descriptor as its two 32-bit halves: the high half
+// (strides, version, swizzle mode) is a constant and the low half (start address >> 4, leading offset)
+// advances by small constants, so the issuing thread spends one integer add per operand instead of
+// rebuilding the descriptor.
+__device__ __forceinline__ void umma_f16_ss_cta1(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_ts_cta1(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// High halves of the two descriptor kinds used with 128-byte swizzle, and the low half for an address.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem_addr)
+{
+    return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem_addr, uint32_t mn_atom_stride)
+{
+    return ((smem_addr & 0x3FFFFu) >> 4) | (((mn_atom_stride >> 4) & 0x3FFFu) << 16);
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]; issued by ONE thread.
 template <int CG>
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,

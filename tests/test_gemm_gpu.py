@@ -109,7 +109,7 @@ def test_ragged_shapes(sp, orc, cuda, shape, cta_group):
 
 @pytest.mark.parametrize("pair", ["tiled_x_identity", "identity_x_tiled", "random_x_random"])
 def test_reference_fixture_pairings_and_comparator(sp, orc, cuda, pair):
-    """The three data styles of gemm/gemm_main.cpp:81-95, judged by the reference's own comparator
+    """The three data styles of gemm/gemm_main.cpp:81-95, checked with the reference's own comparator
     (gemm/gemm_test.cu:131-154) on the device and on the host."""
     M, N, K = 640, 384, 512
     codes = {"tiled_x_identity": (orc.DATA_TILED_NUMBERS, orc.DATA_IDENTITY),

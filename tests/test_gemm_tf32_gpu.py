@@ -64,7 +64,7 @@ def test_tf32_exact_on_fp16_representable_inputs(sp, orc, cuda):
 
 def test_tf32_agrees_with_the_reference_kernels(sp, orc, cuda):
     """Same fp32 inputs through the reference's own matmul_baseline (fp32 FFMA) and matmul_sm80 (mma.sync
-    tf32), compiled unmodified into oracle/_ref, judged by the reference's comparator on non-negative data
+    tf32), compiled unmodified into oracle/_ref, checked with the reference's comparator on non-negative data
     (gemm/gemm_test.cu:131-154)."""
     import torch
 
