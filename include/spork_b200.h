@@ -140,10 +140,12 @@ int spork_gemm_sm100_plan_items(uint32_t M, uint32_t N, uint32_t K, int block_n,
 int spork_gemm_sm100_status(void* stream, uint32_t* detail);
 
 /* Host-buffer convenience (the htod_f32_* pattern of tk_4090_fwd.hpp:7): copies
- * A and B to the device, runs the GEMM, copies C back and synchronises.  A and C
- * move in row chunks on separate copy-in / compute / copy-out streams so that
- * both directions of the host link and the GEMM overlap (pass pinned host
- * memory for that; pageable memory works, serialised).  Device staging buffers,
+ * A and B to the device, runs the GEMM, copies C back and synchronises.  A and B
+ * arrive in alternating row chunks on a copy-in stream; each arrival makes a
+ * strip of C computable, which is multiplied on a compute stream and copied
+ * back on a copy-out stream, so both directions of the host link and the GEMMs
+ * overlap (pass pinned host memory for that; pageable memory works,
+ * serialised).  Device staging buffers,
  * streams and events are created on first use and kept. */
 int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* hA, const void* hB, float* hC);
 

@@ -27,7 +27,7 @@ struct DeviceState {
     void* staging[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t staging_bytes[4] = {0, 0, 0, 0};
     // Copy-in / compute / copy-out streams and hand-over events of the pipelined host-buffer GEMM.
-    static constexpr int kPipeChunks = 16;
+    static constexpr int kPipeChunks = 16;  // chunks of A plus chunks of B
     bool pipe_ready = false;
     cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t pipe_events[2 * kPipeChunks + 1] = {};

@@ -269,7 +269,7 @@ extern "C" int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, 
     const size_t a_bytes = size_t(M) * K * 2, b_bytes = size_t(N) * K * 2, c_bytes = size_t(M) * N * 4;
     if ((rc = spork::ensure_staging(*dev, 0, a_bytes ? a_bytes : 16)) != 0 ||
         (rc = spork::ensure_staging(*dev, 1, b_bytes ? b_bytes : 16)) != 0 ||
-        (rc = spork::ensure_staging(*dev, 2, c_bytes)) != 0) {
+        (rc = spork::ensure_staging(*dev, 2, c_bytes + 1024)) != 0) {
         return rc;
     }
     if (K == 0) {
@@ -279,55 +279,69 @@ extern "C" int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, 
     if ((rc = spork::ensure_pipeline(*dev)) != 0) {
         return rc;
     }
-    // Three streams: copy-in, compute, copy-out.  A and C move in row chunks so that the copy-in of chunk
-    // i+1, the GEMM of chunk i and the copy-out of chunk i-1 overlap (both directions of the host link are
-    // busy at once); B goes first, whole.  With pageable host memory the copies serialise but stay correct.
+    // Three streams: copy-in, compute, copy-out.  A arrives in row chunks and B in row chunks (= column
+    // chunks of C), alternately: A0, B0, A1, B1, ...  Whenever a chunk lands, the strip of C that has just
+    // become computable - the new A chunk against every B chunk present, or every A chunk present against
+    // the new B chunk - is one GEMM into its own contiguous staging block, followed by a pitched copy back
+    // into the caller's C.  Copy-out therefore starts after two chunks instead of after all of B, and both
+    // directions of the host link stay busy.  With pageable host memory the copies serialise but stay correct.
     cudaStream_t s_in = dev->pipe_streams[0], s_comp = dev->pipe_streams[1], s_out = dev->pipe_streams[2];
-    constexpr int kMaxChunks = spork::DeviceState::kPipeChunks;
-    uint32_t chunk_rows = (M + 7) / 8;
-    chunk_rows = (chunk_rows + 255u) / 256u * 256u;  // whole output tiles per chunk
-    uint32_t chunks = (M + chunk_rows - 1) / chunk_rows;
-    if (chunks > (uint32_t)kMaxChunks) {
-        chunks = kMaxChunks;
-        chunk_rows = ((M + chunks - 1) / chunks + 255u) / 256u * 256u;
-        chunks = (M + chunk_rows - 1) / chunk_rows;
-    }
+    constexpr uint32_t kChunksPerSide = spork::DeviceState::kPipeChunks / 2;  // events: one per landed chunk + strip
+    auto chunk_size = [](uint32_t extent) {
+        uint32_t c = (extent + kChunksPerSide - 1) / kChunksPerSide;
+        return (c + 255u) / 256u * 256u;  // whole output tiles per chunk
+    };
+    const uint32_t m_chunk = chunk_size(M), n_chunk = chunk_size(N);
+    const uint32_t m_chunks = (M + m_chunk - 1) / m_chunk, n_chunks = (N + n_chunk - 1) / n_chunk;
     const char* a_host = static_cast<const char*>(hA);
+    const char* b_host = static_cast<const char*>(hB);
     char* a_dev = static_cast<char*>(dev->staging[0]);
+    char* b_dev = static_cast<char*>(dev->staging[1]);
     float* c_dev = static_cast<float*>(dev->staging[2]);
-    cudaEvent_t* ev = dev->pipe_events;  // [0] B ready, [1 + i] A chunk i ready, [1 + kMaxChunks + i] C chunk i ready
-    cudaError_t e = cudaMemcpyAsync(dev->staging[1], hB, b_bytes, cudaMemcpyHostToDevice, s_in);
-    if (e == cudaSuccess) {
-        e = cudaEventRecord(ev[0], s_in);
-    }
-    if (e == cudaSuccess) {
-        e = cudaStreamWaitEvent(s_comp, ev[0], 0);
-    }
-    for (uint32_t i = 0; i < chunks && e == cudaSuccess; ++i) {
-        const uint32_t m0 = i * chunk_rows;
-        const uint32_t rows = M - m0 < chunk_rows ? M - m0 : chunk_rows;
-        const size_t a_off = size_t(m0) * K * 2;
-        e = cudaMemcpyAsync(a_dev + a_off, a_host + a_off, size_t(rows) * K * 2, cudaMemcpyHostToDevice, s_in);
-        if (e == cudaSuccess) {
-            e = cudaEventRecord(ev[1 + i], s_in);
+    cudaEvent_t* ev = dev->pipe_events;  // [2s] chunk of step s landed, [2s + 1] strip of step s computed
+    size_t c_used = 0;                   // floats of the C staging buffer handed out so far
+    uint32_t a_done = 0, b_done = 0;     // chunks of A / B on the device
+    cudaError_t e = cudaSuccess;
+    for (uint32_t step = 0; step < m_chunks + n_chunks && e == cudaSuccess && rc == 0; ++step) {
+        // alternate while both have chunks left; A goes first
+        const bool take_a = a_done < m_chunks && (b_done >= n_chunks || a_done <= b_done);
+        uint32_t sm0, srows, sn0, scols;  // the strip of C this step makes computable
+        if (take_a) {
+            const uint32_t m0 = a_done * m_chunk, rows = M - m0 < m_chunk ? M - m0 : m_chunk;
+            e = cudaMemcpyAsync(a_dev + size_t(m0) * K * 2, a_host + size_t(m0) * K * 2, size_t(rows) * K * 2,
+                                cudaMemcpyHostToDevice, s_in);
+            ++a_done;
+            sm0 = m0, srows = rows, sn0 = 0, scols = b_done * n_chunk < N ? b_done * n_chunk : N;
+        } else {
+            const uint32_t n0 = b_done * n_chunk, rows = N - n0 < n_chunk ? N - n0 : n_chunk;
+            e = cudaMemcpyAsync(b_dev + size_t(n0) * K * 2, b_host + size_t(n0) * K * 2, size_t(rows) * K * 2,
+                                cudaMemcpyHostToDevice, s_in);
+            ++b_done;
+            sm0 = 0, srows = a_done * m_chunk < M ? a_done * m_chunk : M, sn0 = n0, scols = rows;
         }
         if (e == cudaSuccess) {
-            e = cudaStreamWaitEvent(s_comp, ev[1 + i], 0);
+            e = cudaEventRecord(ev[2 * step], s_in);
         }
-        if (e != cudaSuccess) {
-            break;
+        if (e == cudaSuccess) {
+            e = cudaStreamWaitEvent(s_comp, ev[2 * step], 0);
         }
-        rc = spork_gemm_sm100_f16f32(rows, N, K, a_dev + a_off, dev->staging[1], c_dev + size_t(m0) * N, 0, s_comp);
+        if (e != cudaSuccess || srows == 0 || scols == 0) {
+            continue;
+        }
+        float* strip = c_dev + c_used;
+        c_used += (size_t(srows) * scols + 3) & ~size_t(3);  // keep every strip 16-byte aligned
+        rc = spork_gemm_sm100_f16f32(srows, scols, K, a_dev + size_t(sm0) * K * 2, b_dev + size_t(sn0) * K * 2, strip, 0,
+                                     s_comp);
         if (rc) {
             break;
         }
-        e = cudaEventRecord(ev[1 + kMaxChunks + i], s_comp);
+        e = cudaEventRecord(ev[2 * step + 1], s_comp);
         if (e == cudaSuccess) {
-            e = cudaStreamWaitEvent(s_out, ev[1 + kMaxChunks + i], 0);
+            e = cudaStreamWaitEvent(s_out, ev[2 * step + 1], 0);
         }
         if (e == cudaSuccess) {
-            e = cudaMemcpyAsync(hC + size_t(m0) * N, c_dev + size_t(m0) * N, size_t(rows) * N * 4,
-                                cudaMemcpyDeviceToHost, s_out);
+            e = cudaMemcpy2DAsync(hC + size_t(sm0) * N + sn0, size_t(N) * 4, strip, size_t(scols) * 4, size_t(scols) * 4,
+                                  srows, cudaMemcpyDeviceToHost, s_out);
         }
     }
     // Drain all three streams whatever happened, so that the staging buffers are idle on return.

@@ -234,6 +234,18 @@ def test_host_buffer_entry_point(sp, orc, cuda):
     # a second, smaller call reuses the staging buffers
     c2 = sp.matmul_sm100_htod(torch.from_numpy(A[:128].copy()), torch.from_numpy(B))
     assert orc.normalised_error(c2.numpy(), ref[:128], 1.0, 1.0, K) <= TOL
+    # shapes that make the chunk grid ragged in both directions, pinned and pageable host memory
+    for (M2, N2, K2) in ((2300, 2050, 136), (257, 3, 64), (4096, 4100, 72)):
+        A2 = orc.fill_f16(M2, K2, orc.DATA_UNIFORM_PM1, orc.SEED_A)
+        B2 = orc.fill_f16(N2, K2, orc.DATA_UNIFORM_PM1, orc.SEED_B)
+        want = orc.gemm_f16f32(A2, B2)
+        for pin in (False, True):
+            ta, tb = torch.from_numpy(A2), torch.from_numpy(B2)
+            out = torch.full((M2, N2), float("nan"), dtype=torch.float32)
+            if pin:
+                ta, tb, out = ta.pin_memory(), tb.pin_memory(), out.pin_memory()
+            sp.matmul_sm100_htod(ta, tb, out)
+            assert orc.normalised_error(out.numpy(), want, 1.0, 1.0, K2) <= TOL
 
 
 def test_non_default_stream_and_back_to_back_launches(sp, orc, cuda):
