@@ -316,7 +316,14 @@ def main():
 
     for _ in range(args.warmup):
         step()
-    sp.status()
+    if dist is not None:
+        # every rank publishes whether its warm-up launches came back clean; a rank that failed (or never
+        # reports) stops all of them here, before the timed region starts
+        from spork_b200.multi_gpu import RankHealth, default_store
+
+        RankHealth(default_store(), rank, world).guard("warmup", sp.status, timeout_s=120.0)
+    else:
+        sp.status()
 
     # ---- timed region: K launches, one CUDA event pair per launch on the launching stream
     events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]

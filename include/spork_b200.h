@@ -139,6 +139,14 @@ int spork_gemm_sm100_plan_items(uint32_t M, uint32_t N, uint32_t K, int block_n,
  * reference's cudaGetLastError polling (gemm/gemm_test.cu:474-477). */
 int spork_gemm_sm100_status(void* stream, uint32_t* detail);
 
+/* Self-test of the failure-detection path: launches a one-warp kernel that waits,
+ * with the library's bounded wait, on a barrier nothing arrives on.  After
+ * `limit_us` microseconds (1 .. 1,000,000) the wait gives up, the kernel sets the
+ * device status word and returns; the next spork_gemm_sm100_status call then
+ * reports SPORK_ERR_DEVICE_TIMEOUT and the context stays usable.  The reference
+ * spins without bound (gemm/gemm_sm90.cu:434-440) and has no such path. */
+int spork_selftest_bounded_wait(uint32_t limit_us, void* stream);
+
 /* Host-buffer convenience (the htod_f32_* pattern of tk_4090_fwd.hpp:7): copies
  * A and B to the device, runs the GEMM, copies C back and synchronises.  A and B
  * arrive in alternating row chunks on a copy-in stream; each arrival makes a

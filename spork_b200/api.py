@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_f16f32_ex.restype = i32
         L.spork_gemm_sm100_f16f32_static.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
         L.spork_gemm_sm100_f16f32_static.restype = i32
+        L.spork_selftest_bounded_wait.argtypes = [u32, vp]
+        L.spork_selftest_bounded_wait.restype = i32
         L.spork_gemm_sm100_last_clock_mhz.argtypes = [vp, ctypes.POINTER(ctypes.c_double)]
         L.spork_gemm_sm100_last_clock_mhz.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]

@@ -9,6 +9,7 @@
 
 #include "../../include/spork_b200.h"
 #include "device_state.h"
+#include "ptx_sm100.cuh"
 
 namespace spork {
 namespace harness {
@@ -179,8 +180,46 @@ __global__ void compare_kernel(const float* a_mat, const float* b_mat, uint32_t 
     }
 }
 
+// Self-test of the bounded-wait mechanism every kernel of this library relies on: one warp waits, with
+// the same wait routine, on an mbarrier that nothing will ever arrive on.  The wait gives up after
+// `limit_ns`, the status word is set exactly as a stuck production kernel would set it, and the kernel
+// returns normally - the context stays usable.
+__global__ void bounded_wait_selftest_kernel(uint32_t* status, uint64_t limit_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, 0, limit_ns)) {
+            abort_flag = 1;
+            atomicCAS(status, 0u, 0xA0000000u | (blockIdx.x & 0xFFFFu));
+        }
+    }
+    __syncthreads();
+}
+
 }  // namespace harness
 }  // namespace spork
+
+extern "C" int spork_selftest_bounded_wait(uint32_t limit_us, void* stream)
+{
+    if (limit_us == 0 || limit_us > 1000000u) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::DeviceState* dev = nullptr;
+    const int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    spork::harness::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        dev->status_word, uint64_t(limit_us) * 1000ull);
+    return (int)cudaGetLastError();
+}
 
 extern "C" int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
                                         int transpose_rule, void* stream)

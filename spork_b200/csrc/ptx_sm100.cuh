@@ -128,7 +128,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // and not latency critical: fewer issued instructions, less power).
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t backoff_ns = 0)
+                                          uint32_t backoff_ns = 0, uint64_t limit_ns = kWaitLimitNs)
 {
     for (uint32_t fast = 0; fast < 64; ++fast) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) {
@@ -138,7 +138,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             __nanosleep(backoff_ns);
         }
     }
-    const uint64_t deadline = global_timer_ns() + kWaitLimitNs;
+    const uint64_t deadline = global_timer_ns() + limit_ns;
     for (uint32_t spin = 0;; ++spin) {
         if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) {
             return true;
