@@ -197,6 +197,11 @@ int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k,
  * (matrix_util.hpp:40-45) and of launch_tk_4090_fwd_kernel's output. */
 int spork_attn_sm100_fwd_bf16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
                               void* stream);
+/* Every option explicit: bf16 = 0 (fp16) / 1 (bfloat16); causal = 1 masks key j for
+ * query i unless j <= i (key blocks above the diagonal are skipped).  The
+ * reference's math has no mask (torch_attn.py:11-16); causal is an addition. */
+int spork_attn_sm100_fwd_ex(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
+                            int bf16, int causal, void* stream);
 
 /* Reference-shaped FFI entry (tk_4090_fwd.hpp:7, called from
  * torch_attn.py:40-57): HOST fp32 (N, d) arrays, one head, scale 1/sqrt(d). */

@@ -76,6 +76,9 @@ def lib() -> ctypes.CDLL:
         L.spork_oracle_float_to_bf16.argtypes = [ctypes.c_float]
         L.spork_oracle_bf16_to_float.restype = ctypes.c_float
         L.spork_oracle_bf16_to_float.argtypes = [ctypes.c_uint16]
+        L.spork_oracle_attn_ex.restype = ctypes.c_int
+        L.spork_oracle_attn_ex.argtypes = [ctypes.c_int] * 3 + [u16p, u16p, u16p, u16p, f32p, ctypes.c_float,
+                                                                  ctypes.c_int, ctypes.c_int]
         L.spork_oracle_num_threads.restype = ctypes.c_int
         L.spork_oracle_set_threads.argtypes = [ctypes.c_int]
         L.spork_oracle_set_threads.restype = None
@@ -226,3 +229,17 @@ def attn_bf16(q_bits: np.ndarray, k_bits: np.ndarray, v_bits: np.ndarray, scale:
     if rc:
         raise RuntimeError(f"oracle attention failed: {rc}")
     return o16, o32
+
+
+def attn_causal_f16(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float | None = None):
+    """Causal attention (query i sees keys j <= i) on fp16 inputs; returns (o_fp16, o_fp32)."""
+    Q, Kb, V = _as_bits(q), _as_bits(k), _as_bits(v)
+    BH, S, D = Q.shape
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(D))
+    o16 = np.zeros((BH, S, D), dtype=np.uint16)
+    o32 = np.zeros((BH, S, D), dtype=np.float32)
+    rc = lib().spork_oracle_attn_ex(BH, S, D, _u16(Q), _u16(Kb), _u16(V), _u16(o16), _f32(o32), scale, 0, 1)
+    if rc:
+        raise RuntimeError(f"oracle attention failed: {rc}")
+    return o16.view(np.float16), o32

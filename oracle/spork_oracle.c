@@ -433,23 +433,31 @@ ORACLE_API uint64_t spork_oracle_ratio_compare(const float* a_mat, const float* 
 /* single (N, d) problem (matrix_util.hpp:40-45).                              */
 
 static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o16,
-                    float* o32, float scale, int bf16);
+                    float* o32, float scale, int bf16, int causal);
 
 ORACLE_API int spork_oracle_attn_f16(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                                      uint16_t* o16, float* o32, float scale)
 {
-    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 0);
+    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 0, 0);
 }
 
 /* Same with bfloat16 bit patterns in and out (the reference interface's element type). */
 ORACLE_API int spork_oracle_attn_bf16(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v,
                                       uint16_t* o16, float* o32, float scale)
 {
-    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 1);
+    return attn_any(BH, S, D, q, k, v, o16, o32, scale, 1, 0);
+}
+
+/* Causal variant (an addition: the reference's simple_attn has no mask): query i attends to keys j <= i only,
+ * i.e. the softmax and the sum run over the first i + 1 keys. */
+ORACLE_API int spork_oracle_attn_ex(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                    uint16_t* o16, float* o32, float scale, int bf16, int causal)
+{
+    return attn_any(BH, S, D, q, k, v, o16, o32, scale, bf16, causal);
 }
 
 static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o16,
-                    float* o32, float scale, int bf16)
+                    float* o32, float scale, int bf16, int causal)
 {
     if (BH < 0 || S <= 0 || D <= 0) {
         return 2;
@@ -488,8 +496,9 @@ static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, 
                 qrow[d] = bf16 ? bf16_bits_to_float(q[base + (size_t)i * D + d])
                                : half_bits_to_float(q[base + (size_t)i * D + d]);
             }
+            const int keys = causal ? i + 1 : S; /* keys this query attends to */
             float row_max = -INFINITY;
-            for (int j = 0; j < S; ++j) {
+            for (int j = 0; j < keys; ++j) {
                 float acc = 0.0f;
                 for (int d = 0; d < D; ++d) {
                     acc += qrow[d] * kf[(size_t)j * D + d];
@@ -501,14 +510,14 @@ static int attn_any(int BH, int S, int D, const uint16_t* q, const uint16_t* k, 
                 }
             }
             float denom = 0.0f;
-            for (int j = 0; j < S; ++j) {
+            for (int j = 0; j < keys; ++j) {
                 p[j] = expf(p[j] - row_max);
                 denom += p[j];
             }
             for (int d = 0; d < D; ++d) {
                 orow[d] = 0.0f;
             }
-            for (int j = 0; j < S; ++j) {
+            for (int j = 0; j < keys; ++j) {
                 const float pj = p[j] / denom;
                 for (int d = 0; d < D; ++d) {
                     orow[d] += pj * vf[(size_t)j * D + d];

@@ -92,6 +92,8 @@ def lib() -> ctypes.CDLL:
             L.spork_attn_sm100_fwd_f16.restype = i32
             L.spork_attn_sm100_fwd_bf16.argtypes = [i32, i32, i32, vp, vp, vp, vp, ctypes.c_float, vp]
             L.spork_attn_sm100_fwd_bf16.restype = i32
+            L.spork_attn_sm100_fwd_ex.argtypes = [i32, i32, i32, vp, vp, vp, vp, ctypes.c_float, i32, i32, vp]
+            L.spork_attn_sm100_fwd_ex.restype = i32
             L.htod_f32_attn_sm100_fwd.argtypes = [i32, i32, vp, vp, vp, vp]
             L.htod_f32_attn_sm100_fwd.restype = None
         L.spork_b200_version.restype = ctypes.c_char_p
@@ -266,7 +268,7 @@ def compare_f32(x, y, stream=None):
     return first, max_diff
 
 
-def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None):
+def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None, causal: bool = False):
     """o = softmax(q k^T scale) v per head; q, k, v are (BH, S, D) CUDA tensors, all fp16 or all bfloat16
     (the reference interface's type)."""
     import torch
@@ -279,9 +281,9 @@ def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None):
     dt = q.dtype
     if dt not in (torch.float16, torch.bfloat16):
         raise TypeError(f"q must be float16 or bfloat16, got {dt}")
-    fn = lib().spork_attn_sm100_fwd_f16 if dt == torch.float16 else lib().spork_attn_sm100_fwd_bf16
     with torch.cuda.device(q.device):
-        rc = fn(BH, S, D, _dev_ptr(q, dt, "q"), _dev_ptr(k, dt, "k"), _dev_ptr(v, dt, "v"), _dev_ptr(o, dt, "o"),
-                ctypes.c_float(scale), _stream_ptr(stream))
+        rc = lib().spork_attn_sm100_fwd_ex(BH, S, D, _dev_ptr(q, dt, "q"), _dev_ptr(k, dt, "k"), _dev_ptr(v, dt, "v"),
+                                           _dev_ptr(o, dt, "o"), ctypes.c_float(scale), int(dt == torch.bfloat16),
+                                           int(bool(causal)), _stream_ptr(stream))
     _check(rc, "spork_attn_sm100_fwd")
     return o

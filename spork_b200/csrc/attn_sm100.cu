@@ -69,6 +69,7 @@ struct Params {
     int BH, S, D;
     int q_pairs;        // ceil(S / 256): CTAs per head
     int kv_blocks;      // ceil(S / 128)
+    int causal;         // 1: key j contributes to query i only if j <= i
     float scale_log2e;  // scale * log2(e)
     void* o;            // fp16 or bf16, [BH][S][D]
     uint32_t* status;
@@ -131,9 +132,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int head = blockIdx.x / p.q_pairs;
-    const int q_pair = blockIdx.x % p.q_pairs;
+    // causal: the pairs with the most key blocks are launched first, so the short ones fill the tail
+    const int q_pair = p.causal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
     const int q_row0 = q_pair * 2 * kTileQ;
-    const int n_blocks = p.kv_blocks;
+    // causal: keys beyond this CTA's last query row are never needed (both tiles walk the same blocks; the
+    // first tile sees its last block fully masked)
+    const int last_row = q_row0 + 2 * kTileQ - 1 < p.S - 1 ? q_row0 + 2 * kTileQ - 1 : p.S - 1;
+    const int n_blocks = p.causal ? last_row / kTileKV + 1 : p.kv_blocks;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
@@ -333,8 +338,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tmem_ld_32x32b_x32(tmem_s + 96, r3);
                 tmem_ld_wait();
             }
-            const int valid = p.S - j * kTileKV;  // keys of this block that exist
-            if (valid < kTileKV) {                // uniform over the CTA
+            int valid = p.S - j * kTileKV;  // keys of this block that exist
+            bool masked = valid < kTileKV;  // uniform over the CTA
+            if (p.causal) {
+                // keys of this block this row may see: global key index <= global query index
+                const int row_global = q_row0 + (int)w * kTileQ + (int)row;
+                const int seen = row_global - j * kTileKV + 1;
+                valid = seen < valid ? seen : valid;
+                masked = masked || (j + 1) * kTileKV > q_row0 + (int)w * kTileQ + 1;  // uniform over the tile
+            }
+            if (masked) {
 #pragma unroll
                 for (int i = 0; i < 128; ++i) {
                     if (i >= valid) {
@@ -470,8 +483,8 @@ static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int 
 }
 
 template <int D, bool kBf16>
-static int launch(int BH, int S, const void* q, const void* k, const void* v, void* o, float scale, DeviceState& dev,
-                  cudaStream_t stream)
+static int launch(int BH, int S, const void* q, const void* k, const void* v, void* o, float scale, bool causal,
+                  DeviceState& dev, cudaStream_t stream)
 {
     using Cfg = Config<D>;
     auto kernel = attn_fwd_kernel<D, kBf16>;
@@ -490,6 +503,7 @@ static int launch(int BH, int S, const void* q, const void* k, const void* v, vo
     p.D = D;
     p.q_pairs = (S + 2 * kTileQ - 1) / (2 * kTileQ);
     p.kv_blocks = (S + kTileKV - 1) / kTileKV;
+    p.causal = causal ? 1 : 0;
     p.scale_log2e = scale * 1.4426950408889634f;
     p.o = o;
     p.status = dev.status_word;
@@ -530,7 +544,7 @@ extern "C" int spork_attn_sm100_supports(int BH, int S, int D)
 }
 
 static int attn_dispatch(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,
-                         void* stream, bool bf16)
+                         void* stream, bool bf16, bool causal = false)
 {
     if (!spork_attn_sm100_supports(BH, S, D)) {
         return SPORK_ERR_UNSUPPORTED_SHAPE;
@@ -550,11 +564,17 @@ static int attn_dispatch(int BH, int S, int D, const void* q, const void* k, con
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     using namespace spork::attn_sm100;
     if (D == 64) {
-        return bf16 ? launch<64, true>(BH, S, q, k, v, o, scale, *dev, s)
-                    : launch<64, false>(BH, S, q, k, v, o, scale, *dev, s);
+        return bf16 ? launch<64, true>(BH, S, q, k, v, o, scale, causal, *dev, s)
+                    : launch<64, false>(BH, S, q, k, v, o, scale, causal, *dev, s);
     }
-    return bf16 ? launch<128, true>(BH, S, q, k, v, o, scale, *dev, s)
-                : launch<128, false>(BH, S, q, k, v, o, scale, *dev, s);
+    return bf16 ? launch<128, true>(BH, S, q, k, v, o, scale, causal, *dev, s)
+                : launch<128, false>(BH, S, q, k, v, o, scale, causal, *dev, s);
+}
+
+extern "C" int spork_attn_sm100_fwd_ex(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,
+                                       float scale, int bf16, int causal, void* stream)
+{
+    return attn_dispatch(BH, S, D, q, k, v, o, scale, stream, bf16 != 0, causal != 0);
 }
 
 extern "C" int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o,

@@ -118,6 +118,32 @@ def test_bfloat16_golden_vector_of_the_reference_math(sp, cuda):
     assert not (np.abs(got - g["o"]) > ATOL_BF16 + RTOL_BF16 * np.abs(g["o"])).any()
 
 
+@pytest.mark.parametrize("BH,S,D", [(2, 256, 64), (2, 512, 128), (1, 200, 128), (3, 129, 64), (1, 1000, 128), (2, 1, 64)])
+def test_causal_variant_matches_oracle(sp, orc, cuda, BH, S, D):
+    """Causal masking (query i sees keys j <= i) is an addition to the reference's math; key blocks above the
+    diagonal are skipped, the diagonal block is masked per element."""
+    q, k, v = _qkv(sp, cuda, BH, S, D, seed=280)
+    o = sp.attn_fwd(q, k, v, causal=True)
+    sp.status()
+    _, ref = orc.attn_causal_f16(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    ok, worst = _close(o.cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+    # the first query row attends to the first key only: its output is v[0]
+    assert np.abs(o[:, 0].float().cpu().numpy() - v[:, 0].float().cpu().numpy()).max() < 2e-3
+
+
+def test_causal_large_against_torch(sp, cuda):
+    import torch
+
+    BH, S, D = 4, 4096, 128
+    q, k, v = _qkv(sp, cuda, BH, S, D)
+    o = sp.attn_fwd(q, k, v, causal=True)
+    sp.status()
+    ref = torch.nn.functional.scaled_dot_product_attention(q[:2].float(), k[:2].float(), v[:2].float(), is_causal=True)
+    ok, worst = _close(o[:2].cpu().numpy(), ref.cpu().numpy())
+    assert ok, f"max abs error {worst}"
+
+
 def test_softmax_properties_at_larger_sizes(sp, orc, cuda):
     """Sizes the CPU oracle cannot cover in full: (i) V = ones gives O = 1 exactly up to fp16 rounding of P's
     row sums; (ii) attention is invariant to a permutation of the keys/values; (iii) sampled heads against
