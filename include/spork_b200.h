@@ -109,7 +109,9 @@ int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
  * measured best).  stages: shared-memory ring depth, 0 = as deep as fits;
  * group_m: m-tiles per raster group, 0 = default; l2_hints: bit 0 = A loads
  * evict-last, bit 1 = B loads evict-last, bit 2 = B loads evict-first;
- * backoff_ns: sleep between polls of the long waits, 0 = spin.  Bits 4..6 of
+ * backoff_ns: sleep between polls of the long waits, 0 = spin.  Bits 8..9 of
+ * l2_hints: 128-byte column blocks per ring stage (1 or 2; 0 = chosen per shape:
+ * 2 for skinny HBM-bound problems).  Bits 4..6 of
  * l2_hints switch diagnostic experiments whose RESULTS ARE UNDEFINED (0x10 the
  * epilogue drops its stores, 0x20 the producer stops loading after the first
  * ring fill, 0x40 stores go straight from registers).  The reference

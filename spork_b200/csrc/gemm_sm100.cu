@@ -60,13 +60,18 @@ constexpr int kSlabsPerWarp = 2;
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kGroupM = 8;          // raster: m-tiles per group
 
-template <int CG, int BLOCK_N>
+// KATOMS: 128-byte column blocks ("atoms", 64 fp16 along K) per stage.  1 is the default; 2 makes every
+// TMA request of a row 256 contiguous bytes (two adjacent boxes), which serves skinny, HBM-bound shapes
+// better.
+template <int CG, int BLOCK_N, int KATOMS = 1>
 struct Config {
     static constexpr int kUmmaM = kBlockM * CG;
     static constexpr int kUmmaN = BLOCK_N;
     static constexpr int kBRows = BLOCK_N / CG;  // rows of B this CTA loads per stage
-    static constexpr int kABytes = kBlockM * kBlockK * 2;
-    static constexpr int kBBytes = kBRows * kBlockK * 2;
+    static constexpr int kAtomABytes = kBlockM * kBlockK * 2;
+    static constexpr int kAtomBBytes = kBRows * kBlockK * 2;
+    static constexpr int kABytes = KATOMS * kAtomABytes;
+    static constexpr int kBBytes = KATOMS * kAtomBBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStagingBytes = kNumEpilogueWarps * kSlabsPerWarp * kSlabBytes;
     static constexpr int kBarrierBytes = 1024;
@@ -193,12 +198,12 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
 // kWorkspace = true: each K split stores its partial tile into slab `split` of a
 // [split][M][N] fp32 workspace (tmap_c is then a 3-D map over it) instead of
 // writing or reduce-adding into C; a second kernel sums the slabs in a fixed order.
-template <int CG, int BLOCK_N, bool kWorkspace = false, bool kTf32 = false>
+template <int CG, int BLOCK_N, bool kWorkspace = false, bool kTf32 = false, int KATOMS = 1>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_c, const Params p)
 {
-    using Cfg = Config<CG, BLOCK_N>;
+    using Cfg = Config<CG, BLOCK_N, KATOMS>;
     extern __shared__ uint8_t smem_raw[];
 
     const uint32_t warp = threadIdx.x / 32;
@@ -283,16 +288,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     } else if (CG == 1) {
                         mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-                        tma_load_2d_hint(sa, &tmap_a, full, (int32_t)(kb * kElemsK), a_row, pol_a);
-                        tma_load_2d_hint(sb, &tmap_b, full, (int32_t)(kb * kElemsK), b_row, pol_b);
+#pragma unroll
+                        for (int at = 0; at < KATOMS; ++at) {
+                            const int32_t x = (int32_t)((kb * KATOMS + at) * kElemsK);
+                            tma_load_2d_hint(sa + at * Cfg::kAtomABytes, &tmap_a, full, x, a_row, pol_a);
+                            tma_load_2d_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, full, x, b_row, pol_b);
+                        }
                     } else {
                         // Both CTAs' bytes complete on the leader's barrier.
                         if (is_leader) {
                             mbar_arrive_expect_tx(full, Cfg::kStageBytes * 2);
                         }
                         const uint32_t leader_full = map_to_cta(full, 0);
-                        tma_load_2d_pair_hint(sa, &tmap_a, leader_full, (int32_t)(kb * kElemsK), a_row, pol_a);
-                        tma_load_2d_pair_hint(sb, &tmap_b, leader_full, (int32_t)(kb * kElemsK), b_row, pol_b);
+#pragma unroll
+                        for (int at = 0; at < KATOMS; ++at) {
+                            const int32_t x = (int32_t)((kb * KATOMS + at) * kElemsK);
+                            tma_load_2d_pair_hint(sa + at * Cfg::kAtomABytes, &tmap_a, leader_full, x, a_row, pol_a);
+                            tma_load_2d_pair_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, leader_full, x, b_row, pol_b);
+                        }
                     }
                     ++issued;
                     if (++stage == p.stages) {
@@ -329,17 +342,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                     tcgen05_fence_after();
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
-                    const uint64_t desc_a = umma_desc_kmajor_sw128(sa);
-                    const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes);
 #pragma unroll
-                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the (>>4) address field.
-                        if (kTf32) {
-                            umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
-                                             (kb != w.kb_begin || k != 0) ? 1u : 0u);
-                        } else {
-                            umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
-                                            (kb != w.kb_begin || k != 0) ? 1u : 0u);
+                    for (int at = 0; at < KATOMS; ++at) {
+                        const uint64_t desc_a = umma_desc_kmajor_sw128(sa + at * Cfg::kAtomABytes);
+                        const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes + at * Cfg::kAtomBBytes);
+#pragma unroll
+                        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                            // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the (>>4) address field.
+                            const uint32_t acc = (kb != w.kb_begin || at != 0 || k != 0) ? 1u : 0u;
+                            if (kTf32) {
+                                umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                            } else {
+                                umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                            }
                         }
                     }
                     // Free the stage (in both CTAs) once these MMAs have read it.
@@ -597,15 +612,16 @@ struct Tuning {
     int l2_hints = 0;
     int backoff_ns = 0;
     int experiment = 0;
+    int k_atoms = 0;      // 0 = choose; 1 / 2 = 128-byte column blocks per stage
 };
 static Tuning g_tuning;
 
-template <int CG, int BLOCK_N, bool kTf32 = false>
+template <int CG, int BLOCK_N, bool kTf32 = false, int KATOMS = 1>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
                   int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false)
 {
-    using Cfg = Config<CG, BLOCK_N>;
-    auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32>;
+    using Cfg = Config<CG, BLOCK_N, KATOMS>;
+    auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS>;
     constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
     constexpr CUtensorMapDataType kOperandType = kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     constexpr uint32_t kOperandBytes = kTf32 ? 4 : 2;
@@ -622,7 +638,8 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
 
     Params p{};
     uint32_t groups = 1;
-    plan_launch(p, groups, M, N, K, Cfg::kUmmaM, BLOCK_N, CG, kElemsK, split_k, stream_k, max_ctas, dev.sm_count);
+    plan_launch(p, groups, M, N, K, Cfg::kUmmaM, BLOCK_N, CG, kElemsK * KATOMS, split_k, stream_k, max_ctas,
+                dev.sm_count);
     p.C = C;
     p.status = dev.status_word;
     const Tuning tune = g_tuning;
@@ -714,6 +731,20 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     }
     const bool stream_k = split_k == -1;
     const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
+    // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
+    // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.
+    const uint64_t out_tiles = (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n);
+    const bool wide_k = !tf32 && cta_group == 2 &&
+                        (g_tuning.k_atoms == 2 || (g_tuning.k_atoms == 0 && block_n <= 128 &&
+                                                   out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
+    if (wide_k) {
+        switch (block_n) {
+        case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        default: return SPORK_ERR_BAD_ARGUMENT;
+        }
+    }
 #define SPORK_GEMM_CASE(CG_, BN_)                                                               \
     if (cta_group == CG_ && block_n == BN_) {                                                   \
         return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);        \
@@ -1055,10 +1086,11 @@ extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x7F || backoff_ns < 0 || backoff_ns > 100000) {
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x2FF || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
-    spork::gemm_sm100::g_tuning.experiment = l2_hints >> 4;  // bits 4..6: diagnostic experiments (see Params)
+    spork::gemm_sm100::g_tuning.experiment = (l2_hints >> 4) & 7;  // bits 4..6: diagnostic experiments (see Params)
+    spork::gemm_sm100::g_tuning.k_atoms = l2_hints >> 8;           // bits 8..9: column blocks per stage, 0 = choose
     l2_hints &= 7;
     spork::gemm_sm100::g_tuning.stages = stages;
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;

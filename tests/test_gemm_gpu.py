@@ -167,6 +167,23 @@ def test_stream_k(sp, orc, cuda, shape):
         _check(sp, orc, a, b, c, K)
 
 
+@pytest.mark.parametrize("shape", [(16384, 64, 2048), (1000, 264, 136), (513, 128, 4104), (256, 256, 64), (300, 131, 200)])
+def test_two_column_blocks_per_stage(sp, orc, cuda, shape):
+    """The ring-stage variant chosen for skinny problems (256-byte row segments per TMA request), forced on
+    shapes with ragged K so that the zero-filled tail spans a whole column block."""
+    M, N, K = shape
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    try:
+        sp.tune(l2_hints=0x200)
+        for block_n, split_k in ((64, 1), (128, 2), (256, -1)):
+            c = _poisoned(cuda, M, N)
+            sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=2, split_k=split_k)
+            sp.status()
+            _check(sp, orc, a, b, c, K)
+    finally:
+        sp.tune()
+
+
 def test_n_not_multiple_of_four_uses_guarded_stores(sp, orc, cuda):
     for M, N, K in ((130, 67, 72), (256, 1, 64), (300, 131, 136)):
         a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
