@@ -99,10 +99,12 @@ int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A
 int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                    int split_k, void* stream);
 
-/* SM clock (MHz) the most recent GEMM launch on the current device really ran at:
- * its first CTA notes SM cycles and wall-clock time at both ends of the launch.
- * Synchronises `stream`.  Under the power cap this is far below the nominal
- * clock that the management library reports.  No counterpart in the reference. */
+/* SM clock (MHz) the most recent GEMM or attention launch on the current device
+ * really ran at: one CTA (the first of a GEMM, which lives as long as the launch;
+ * the last of an attention launch) notes SM cycles and wall-clock time at both
+ * ends of its life.  Synchronises `stream`.  Under the power cap this is far below
+ * the nominal clock that the management library reports.  No counterpart in the
+ * reference. */
 int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
 
 /* Process-wide tuning of later launches (benchmark sweeps; the defaults are the

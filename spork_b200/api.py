@@ -184,7 +184,7 @@ def matmul_sm100_tf32(a, b, c=None, *, variant: int = 0, split_k: int = 1, strea
 
 
 def last_clock_mhz(stream=None) -> float:
-    """SM clock the most recent GEMM launch on the current device ran at (measured inside the kernel)."""
+    """SM clock the most recent GEMM or attention launch on the current device ran at (measured inside the kernel)."""
     mhz = ctypes.c_double(0.0)
     _check(lib().spork_gemm_sm100_last_clock_mhz(_stream_ptr(stream), ctypes.byref(mhz)), "last_clock_mhz")
     return float(mhz.value)

@@ -12,14 +12,19 @@
 //   warps 4-7  softmax of query tile 1
 //   warp  8    TMA producer (Q tiles once, then K_j, V_j through a ring)
 //   warp  9    tcgen05.mma issuer (one thread) and TMEM owner
+//   warps 10-11 idle: they complete the third warpgroup, so that whole warpgroups can trade
+//              registers (setmaxnreg): 216 per softmax thread, 72 for the rest
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
 // Per key block j and query tile w:
 //   S_w = Q_w K_j^T            tcgen05.mma, both operands K-major in shared memory
 //   softmax thread: reads its whole S row into registers, row max,
 //       p = exp2((s - m) * scale*log2e), row sum; P_w (fp16, two per column) is
-//       written back into tensor memory over the first 64 columns of S_w;
-//       O_w is rescaled in place (tcgen05.ld/st) only when the row max grew by
-//       more than 2^8 since the last rescale (p then stays within fp16 range)
+//       written back into tensor memory over the first 64 columns of S_w and handed to the
+//       issuer in two halves of 64 keys, so the first half is multiplied while the second is
+//       still being exponentiated;
+//       O_w is rescaled in place (tcgen05.ld/st), before the first half is handed over, only
+//       when the row max grew by more than 2^8 since the last rescale (p then stays within
+//       fp16 range)
 //   O_w += P_w V_j             tcgen05.mma, A = P_w from tensor memory, B = V_j (N-major)
 // The two query tiles alternate, so the tensor core works on one tile while the
 // other tile's softmax runs.  Keys past the end of a ragged sequence are masked
@@ -46,11 +51,17 @@ using namespace ptx;
 
 constexpr int kTileQ = 128;     // query rows per tile (= TMEM lanes)
 constexpr int kTileKV = 128;    // keys per block
-constexpr int kNumThreads = 320;
+constexpr int kNumThreads = 384;     // 8 softmax warps, the TMA warp, the MMA warp, two idle warps that complete the third warpgroup
+constexpr int kSoftmaxRegs = 216;    // registers per thread after the warpgroups trade: 2*128*232 + 128*40 <= 64 Ki
+constexpr int kOtherRegs = 72;
+// setmaxnreg.inc waits, without a limit, for registers to be free: the trade must fit the allocation the
+// CTA was launched with (kNumThreads * 168), not the whole file
+static_assert(2 * kSoftmaxRegs + kOtherRegs <= 3 * 168, "register trade exceeds the launch allocation");
 constexpr int kLoadWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kMaxKvStages = 8;
 constexpr int kTmemCols = 512;
+constexpr uint32_t kSoftmaxBackoffNs = 20;  // the softmax warps' waits sleep between polls
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by more than 2^8
 
 template <int D>
@@ -80,7 +91,7 @@ struct Barriers {
     uint64_t kv_full[kMaxKvStages];
     uint64_t kv_empty[kMaxKvStages];
     uint64_t s_full[2];
-    uint64_t p_ready[2];
+    uint64_t p_ready[2][2];  // [query tile][key half]
     uint64_t pv_done[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -89,8 +100,16 @@ struct Barriers {
 __device__ __forceinline__ float ex2_approx(float x)
 {
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Largest of three: one instruction of the 16-lane integer/logic pipe where two-input max needs two.
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 
 // Two fp32 values rounded to a packed pair of 16-bit floats (low half first): fp16 or bf16.
@@ -131,6 +150,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         reinterpret_cast<Barriers*>(smem_raw + (kv_smem + kKvStages * Cfg::kTileBytes - smem_u32(smem_raw)));
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
+    // Clock probe: the last CTA notes SM cycles and wall-clock nanoseconds at both ends of its life; their
+    // ratio is the SM clock this launch really ran at late in its run (read by spork_gemm_sm100_last_clock_mhz).
+    unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
+
     const int head = blockIdx.x / p.q_pairs;
     // causal: the pairs with the most key blocks are launched first, so the short ones fill the tail
     const int q_pair = p.causal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
@@ -148,7 +175,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         for (int w = 0; w < 2; ++w) {
             mbar_init(smem_u32(&bars->s_full[w]), 1);
-            mbar_init(smem_u32(&bars->p_ready[w]), kTileQ);
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(smem_u32(&bars->p_ready[w][h]), kTileQ);
+            }
             mbar_init(smem_u32(&bars->pv_done[w]), 1);
         }
         bars->abort_flag = 0;
@@ -171,7 +200,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128; P_w (fp16 pairs) reuses its first 64 columns
     const uint32_t tmem_o0 = tmem_base + 256;    // O_w at + w * 128
 
-    if (warp == kLoadWarp) {
+    // The softmax keeps a whole row of 128 scores in registers and needs room beside them to overlap
+    // the exponentials' latencies; the loader and the issuer need almost none. Whole warpgroups trade.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+        if (warp == kLoadWarp) {
         // ---------------------------------------------------------- TMA producer
         if (lane == 0) {
             const uint32_t qf = smem_u32(&bars->q_full);
@@ -222,7 +255,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
             // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
             const uint32_t q_lo[2] = {desc_lo_kmajor(q_smem), desc_lo_kmajor(q_smem + Cfg::kTileBytes)};
-            // S_w = Q_w K^T from the K tile in ring slot `st`
+            // S_w = Q_w K^T from the K tile in ring slot `st`. (Not split along the keys: with both operands
+            // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
             auto issue_qk = [&](int w, uint32_t st) {
                 const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
 #pragma unroll
@@ -231,13 +265,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo[w] + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
                                      kk != 0 ? 1u : 0u);
                 }
+                umma_commit<1>(smem_u32(&bars->s_full[w]));
             };
             // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
             // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart)
-            auto issue_pv = [&](int w, uint32_t st, bool accumulate) {
+            auto issue_pv = [&](int w, uint32_t st, bool accumulate, int h) {
                 const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
 #pragma unroll
-                for (int kk = 0; kk < kTileKV / 16; ++kk) {
+                for (int kk = h * (kTileKV / 32); kk < (h + 1) * (kTileKV / 32); ++kk) {
                     umma_f16_ts_cta1(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
                                      kDescHiSw128, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
                 }
@@ -255,7 +290,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tcgen05_fence_after();
                 for (int w = 0; w < 2; ++w) {
                     issue_qk(w, stage);
-                    umma_commit<1>(smem_u32(&bars->s_full[w]));
                 }
                 umma_commit<1>(smem_u32(&bars->kv_empty[stage]));
                 advance();
@@ -268,7 +302,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                         advance();
                     }
                     for (int w = 0; w < 2 && ok; ++w) {
-                        if (!mbar_wait(smem_u32(&bars->p_ready[w]), (uint32_t)(j & 1), abort_flag)) {
+                        if (!mbar_wait(smem_u32(&bars->p_ready[w][0]), (uint32_t)(j & 1), abort_flag)) {
                             report_timeout(p, abort_flag, 2, 0x30 + w);
                             ok = false;
                             break;
@@ -279,7 +313,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             break;
                         }
                         tcgen05_fence_after();
-                        issue_pv(w, v_stage, j > 0);
+                        issue_pv(w, v_stage, j > 0, 0);   // the first 64 keys, while the softmax does the rest
+                        if (!mbar_wait(smem_u32(&bars->p_ready[w][1]), (uint32_t)(j & 1), abort_flag)) {
+                            report_timeout(p, abort_flag, 2, 0x38 + w);
+                            ok = false;
+                            break;
+                        }
+                        tcgen05_fence_after();
+                        issue_pv(w, v_stage, true, 1);
                         if (!more) {
                             umma_commit<1>(smem_u32(&bars->pv_done[w]));  // completes once: O_w is final
                         }
@@ -294,7 +335,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             }
                             tcgen05_fence_after();
                             issue_qk(w, k_stage);
-                            umma_commit<1>(smem_u32(&bars->s_full[w]));
                             if (w == 1) {
                                 umma_commit<1>(smem_u32(&bars->kv_empty[k_stage]));
                             }
@@ -303,8 +343,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 }
             } while (false);
         }
+        }
     } else {
         // --------------------------------------------------------------- softmax
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         const uint32_t w = warp / 4;        // query tile of this warpgroup
         const uint32_t quarter = warp % 4;  // TMEM lanes [32*quarter, +32)
         const uint32_t row = quarter * 32 + lane;
@@ -316,15 +358,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         float l_run = 0.0f;       // running row sum
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
-            if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, 20)) {
+            if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, kSoftmaxBackoffNs)) {
                 if (lane == 0) {
                     report_timeout(p, abort_flag, 3, 0x10 + w);
                 }
                 ok = false;
                 break;
             }
-            // s_full also means every earlier MMA of the issuing thread is complete: P_w of the previous
-            // block has been consumed and O_w is not being written.
+            // A completed s_full also means every earlier MMA of the issuing thread is complete: P_w of the
+            // previous block has been consumed and O_w is not being written.
             tcgen05_fence_after();
             uint32_t r[128];
             {
@@ -355,17 +397,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     }
                 }
             }
-            float m_blk = __uint_as_float(r[0]);
+            // four independent chains of three-input max
+            float m4[4] = {__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]),
+                           __uint_as_float(r[3])};
 #pragma unroll
-            for (int i = 1; i < 128; ++i) {
-                m_blk = fmaxf(m_blk, __uint_as_float(r[i]));
+            for (int i = 4; i < 124; i += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    m4[c] = max3(m4[c], __uint_as_float(r[i + 2 * c]), __uint_as_float(r[i + 2 * c + 1]));
+                }
             }
+            m4[0] = max3(m4[0], __uint_as_float(r[124]), __uint_as_float(r[125]));
+            m4[1] = max3(m4[1], __uint_as_float(r[126]), __uint_as_float(r[127]));
+            const float m_blk = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
             // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
             const bool grow = j == 0 || (m_blk - m_ref) * sl2 > kRescaleThreshold;
             float alpha = 1.0f;
             if (grow) {
                 alpha = ex2_approx((m_ref - m_blk) * sl2);  // 0 on the first block
                 m_ref = m_blk;
+            }
+            // Rescale O_w when some row of this warp moved its reference max (never on the first block).
+            // It has to be finished before the first half of P is handed over: from then on the issuer
+            // accumulates into O_w.
+            if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32b_x32(tmem_o + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    }
+                    tmem_st_32x32b_x32(tmem_o + c * 32, o);
+                }
             }
             const float neg_m = -m_ref * sl2;
             float l_blk0 = 0.0f, l_blk1 = 0.0f;
@@ -381,25 +447,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     packed[i] = pack_half2<kBf16>(p0, p1);
                 }
                 tmem_st_32x32b_x32(tmem_s + half * 32, packed);
+                // hand this half of P_w over: the issuer multiplies it while the other half is computed
+                tmem_st_wait();
+                tcgen05_fence_before();
+                mbar_arrive(smem_u32(&bars->p_ready[w][half]));
             }
             l_run = l_run * alpha + (l_blk0 + l_blk1);
-            // rescale O_w when some row of this warp moved its reference max (never on the first block)
-            if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
-#pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(tmem_o + c * 32, o);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    }
-                    tmem_st_32x32b_x32(tmem_o + c * 32, o);
-                }
-            }
-            tmem_st_wait();
-            tcgen05_fence_before();
-            mbar_arrive(smem_u32(&bars->p_ready[w]));
         }
         // ---- epilogue: O_w / l -> fp16 -> global
         if (ok) {
@@ -441,6 +494,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (warp == kMmaWarp) {
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        probe[2] = (unsigned long long)clock64();
+        probe[3] = global_timer_ns();
     }
 }
 
