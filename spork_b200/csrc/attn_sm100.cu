@@ -139,7 +139,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 {
     using Cfg = Config<D>;
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t warp = threadIdx.x / 32;
+    const uint32_t warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);  // provably the same in all lanes
     const uint32_t lane = threadIdx.x % 32;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -240,109 +240,125 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false, kBf16);
-            constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true, kBf16);  // B = V is N-major
-            uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
-            bool ok = true;
-            auto advance = [&]() {
-                if (++stage == (uint32_t)kKvStages) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
-            };
-            // Descriptor low words: one per operand tile, advanced by compile-time constants per MMA
-            // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
-            // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
-            const uint32_t q_lo[2] = {desc_lo_kmajor(q_smem), desc_lo_kmajor(q_smem + Cfg::kTileBytes)};
-            // S_w = Q_w K^T from the K tile in ring slot `st`. (Not split along the keys: with both operands
-            // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
-            auto issue_qk = [&](int w, uint32_t st) {
-                const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
+        // The whole warp runs the control flow and one elected lane issues. Everything an issue needs
+        // (descriptors, tensor-memory and barrier addresses) is then the same in all lanes and can live in
+        // uniform registers; issued from inside a one-lane branch each multiply cost the thread about
+        // 60 cycles, as long as the tensor core needs to execute it, and the issuer bounded the kernel.
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false, kBf16);
+        constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true, kBf16);  // B = V is N-major
+        uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
+        bool ok = true;
+        auto advance = [&]() {
+            if (++stage == (uint32_t)kKvStages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        };
+        // Descriptor low words: one per operand tile, advanced by compile-time constants per MMA
+        // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
+        // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
+        const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
+        // S_w = Q_w K^T from the K tile in ring slot `st`. (Not split along the keys: with both operands
+        // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
+        auto issue_qk = [&](int w, uint32_t st) {
+            const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
+            const uint32_t q_lo = q_lo0 + (uint32_t)w * (Cfg::kTileBytes >> 4);
+            if (leader) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (uint32_t)((kk / 4) * (Cfg::kAtomBytes >> 4) + 2 * (kk % 4));
-                    umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo[w] + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
+                    umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
                                      kk != 0 ? 1u : 0u);
                 }
                 umma_commit<1>(smem_u32(&bars->s_full[w]));
-            };
-            // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
-            // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart)
-            auto issue_pv = [&](int w, uint32_t st, bool accumulate, int h) {
-                const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
+            }
+        };
+        // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
+        // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart);
+        // half h covers keys [64 h, 64 h + 64)
+        auto issue_pv = [&](int w, uint32_t st, bool accumulate, int h) {
+            const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
+            if (leader) {
 #pragma unroll
                 for (int kk = h * (kTileKV / 32); kk < (h + 1) * (kTileKV / 32); ++kk) {
                     umma_f16_ts_cta1(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
                                      kDescHiSw128, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
                 }
-            };
-            do {
-                if (!mbar_wait(smem_u32(&bars->q_full), 0, abort_flag)) {
-                    report_timeout(p, abort_flag, 2, 0x20);
-                    break;
-                }
-                // prologue: S_0(0), S_1(0)
-                if (!mbar_wait(smem_u32(&bars->kv_full[stage]), phase, abort_flag)) {
-                    report_timeout(p, abort_flag, 2, stage);
-                    break;
-                }
-                tcgen05_fence_after();
-                for (int w = 0; w < 2; ++w) {
-                    issue_qk(w, stage);
-                }
-                umma_commit<1>(smem_u32(&bars->kv_empty[stage]));
+            }
+        };
+        auto commit = [&](uint64_t* bar) {
+            if (leader) {
+                umma_commit<1>(smem_u32(bar));
+            }
+        };
+        // every lane polls; a timeout is reported once
+        auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t where) {
+            const bool done = mbar_wait(smem_u32(bar), parity, abort_flag);
+            if (!done && leader) {
+                report_timeout(p, abort_flag, 2, where);
+            }
+            return __all_sync(0xFFFFFFFFu, done);
+        };
+        do {
+            if (!wait(&bars->q_full, 0, 0x20)) {
+                break;
+            }
+            // prologue: S_0(0), S_1(0)
+            if (!wait(&bars->kv_full[stage], phase, stage)) {
+                break;
+            }
+            tcgen05_fence_after();
+            issue_qk(0, stage);
+            issue_qk(1, stage);
+            commit(&bars->kv_empty[stage]);
+            advance();
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const uint32_t v_stage = stage, v_phase = phase;
                 advance();
-                for (int j = 0; j < n_blocks && ok; ++j) {
-                    const uint32_t v_stage = stage, v_phase = phase;
+                const uint32_t k_stage = stage, k_phase = phase;  // K_{j+1}, if any
+                const bool more = j + 1 < n_blocks;
+                if (more) {
                     advance();
-                    const uint32_t k_stage = stage, k_phase = phase;  // K_{j+1}, if any
-                    const bool more = j + 1 < n_blocks;
-                    if (more) {
-                        advance();
+                }
+                // The tiles this block's multiplies read were requested long ago; make sure of them now, while
+                // the softmax is still at work, so that nothing stands between P arriving and the issue.
+                if (!wait(&bars->kv_full[v_stage], v_phase, v_stage) ||
+                    (more && !wait(&bars->kv_full[k_stage], k_phase, k_stage))) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    if (!ok) {
+                        break;
                     }
-                    for (int w = 0; w < 2 && ok; ++w) {
-                        if (!mbar_wait(smem_u32(&bars->p_ready[w][0]), (uint32_t)(j & 1), abort_flag)) {
-                            report_timeout(p, abort_flag, 2, 0x30 + w);
-                            ok = false;
-                            break;
-                        }
-                        if (w == 0 && !mbar_wait(smem_u32(&bars->kv_full[v_stage]), v_phase, abort_flag)) {
-                            report_timeout(p, abort_flag, 2, v_stage);
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        issue_pv(w, v_stage, j > 0, 0);   // the first 64 keys, while the softmax does the rest
-                        if (!mbar_wait(smem_u32(&bars->p_ready[w][1]), (uint32_t)(j & 1), abort_flag)) {
-                            report_timeout(p, abort_flag, 2, 0x38 + w);
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        issue_pv(w, v_stage, true, 1);
-                        if (!more) {
-                            umma_commit<1>(smem_u32(&bars->pv_done[w]));  // completes once: O_w is final
-                        }
-                        if (w == 1) {
-                            umma_commit<1>(smem_u32(&bars->kv_empty[v_stage]));
-                        }
+                    if (!wait(&bars->p_ready[w][0], (uint32_t)(j & 1), 0x30 + w)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    issue_pv(w, v_stage, j > 0, 0);  // the first 64 keys, while the softmax does the rest
+                    if (!wait(&bars->p_ready[w][1], (uint32_t)(j & 1), 0x38 + w)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    issue_pv(w, v_stage, true, 1);
+                    if (more) {
+                        issue_qk(w, k_stage);
+                    } else {
+                        commit(&bars->pv_done[w]);  // completes once: O_w is final
+                    }
+                    if (w == 1) {
+                        commit(&bars->kv_empty[v_stage]);
                         if (more) {
-                            if (w == 0 && !mbar_wait(smem_u32(&bars->kv_full[k_stage]), k_phase, abort_flag)) {
-                                report_timeout(p, abort_flag, 2, k_stage);
-                                ok = false;
-                                break;
-                            }
-                            tcgen05_fence_after();
-                            issue_qk(w, k_stage);
-                            if (w == 1) {
-                                umma_commit<1>(smem_u32(&bars->kv_empty[k_stage]));
-                            }
+                            commit(&bars->kv_empty[k_stage]);
                         }
                     }
                 }
-            } while (false);
-        }
+            }
+        } while (false);
         }
     } else {
         // --------------------------------------------------------------- softmax

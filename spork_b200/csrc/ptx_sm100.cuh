@@ -32,6 +32,20 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 
 // ---------------------------------------------------------------- cluster ---
 
+// One lane of a converged warp (the same one every time).
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
     uint32_t r;
