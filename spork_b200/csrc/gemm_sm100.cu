@@ -206,7 +206,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     using Cfg = Config<CG, BLOCK_N, KATOMS>;
     extern __shared__ uint8_t smem_raw[];
 
-    const uint32_t warp = threadIdx.x / 32;
+    const uint32_t warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);  // provably the same in all lanes
     const uint32_t lane = threadIdx.x % 32;
     const uint32_t cta_rank = CG == 2 ? cluster_ctarank() : 0u;
     const bool is_leader = cta_rank == 0;
@@ -317,7 +317,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        if (lane == 0 && is_leader) {
+        // The whole warp runs the control flow and one elected lane issues: descriptors, tensor-memory
+        // and barrier addresses are then the same in all lanes and can live in uniform registers, which
+        // makes an issue a few instructions instead of some sixty cycles from inside a one-lane branch.
+        if (is_leader) {
+            const bool elected = elect_one();
             constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32_f32(Cfg::kUmmaM, Cfg::kUmmaN)
                                              : umma_idesc_f16_f32(Cfg::kUmmaM, Cfg::kUmmaN);
             uint32_t stage = 0, phase = 0;
@@ -327,21 +331,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const WorkItem w = group_item(p, group_id, num_groups, item);
                 const uint32_t buf = local & 1u;
                 const uint32_t acc_phase = (local >> 1) & 1u;
-                if (!mbar_wait<CG == 2>(smem_u32(&bars->tmem_empty[buf]), acc_phase ^ 1u, abort_flag)) {
-                    report_timeout(p, abort_flag, 2, 0x40 + buf);
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait<CG == 2>(smem_u32(&bars->tmem_empty[buf]), acc_phase ^ 1u,
+                                                                abort_flag))) {
+                    if (elected) {
+                        report_timeout(p, abort_flag, 2, 0x40 + buf);
+                    }
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * Cfg::kAccCols;
                 for (uint32_t kb = w.kb_begin; kb < w.kb_end; ++kb) {
-                    if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
-                        report_timeout(p, abort_flag, 2, stage);
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag))) {
+                        if (elected) {
+                            report_timeout(p, abort_flag, 2, stage);
+                        }
                         ok = false;
                         break;
                     }
                     tcgen05_fence_after();
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
+                    if (elected) {
 #pragma unroll
                     for (int at = 0; at < KATOMS; ++at) {
                         const uint64_t desc_a = umma_desc_kmajor_sw128(sa + at * Cfg::kAtomABytes);
@@ -363,6 +373,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (CG == 2) {
                         umma_commit<CG>(map_to_cta(empty, 1));
                     }
+                    }
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1u;
@@ -373,9 +384,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
                 // Accumulator complete: wake the epilogue warps (of both CTAs).
                 const uint32_t tfull = smem_u32(&bars->tmem_full[buf]);
-                umma_commit<CG>(tfull);
-                if (CG == 2) {
-                    umma_commit<CG>(map_to_cta(tfull, 1));
+                if (elected) {
+                    umma_commit<CG>(tfull);
+                    if (CG == 2) {
+                        umma_commit<CG>(map_to_cta(tfull, 1));
+                    }
                 }
             }
         }
