@@ -64,6 +64,22 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
     return rc;
 }
 
+// L independent products in one launch; `t` describes one of them and the L matrices of each operand
+// follow one another in memory: the batch dimension of the reference's generated entry points
+// (xgemm_Sm90.py:45-48, called with L = 1 at gemm/gemm_test.cu:310-362).
+inline int matmul_sm100_batched(uint32_t L, GPU_TensorsF16 t, cudaStream_t stream, int split_k = 1, int variant = 0)
+{
+    if (!matmul_sm100_supports(t)) {
+        fprintf(stderr, "matmul_sm100_batched: unsupported layout or K %% 8 != 0 (M=%u N=%u K=%u)\n", t.M, t.N, t.K);
+        return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    const int rc = spork_gemm_sm100_f16f32_batched(L, t.M, t.N, t.K, t.a, t.b, t.c, variant, split_k, stream);
+    if (rc != 0) {
+        fprintf(stderr, "matmul_sm100_batched: error %d\n", rc);
+    }
+    return rc;
+}
+
 // Drop-in for the reference's own descriptor type: `Tensors` is any by-value struct with the fields of
 // GPU_Tensors (gemm/gpu_tensor.h:9-21: M, N, K, float const* a, b, float* c, a_col_major, b_col_major,
 // c_col_major), so `matmul_sm100_tf32(t, stream)` can stand where `matmul_sm90(t, mode, stream)`

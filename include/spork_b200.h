@@ -79,6 +79,19 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
 int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                int block_n, int cta_group, int split_k, int max_ctas, void* stream);
 
+/* A batch of L independent products in one launch: C[l] = A[l] * B[l]^T with
+ * A [L][M][K], B [L][N][K] (fp16) and C [L][M][N] (fp32) each stored as L
+ * contiguous row-major matrices.  The counterpart of the batch dimension `L` of
+ * the reference's generated entry points (xgemm_Sm90.py:45-48, C: f32[L,N,M];
+ * call sites gemm/gemm_test.cu:310-362 pass L = 1); a caller with that
+ * column-major C swaps the operands, as for the single product.  The kernel is
+ * the same persistent kernel: the batch index is one more coordinate of the tile
+ * scheduler and of 3-D tensor maps, so ragged M and N are zero-filled and
+ * clipped per matrix.  `variant` as for spork_gemm_sm100_f16f32; split_k >= 1 as
+ * for the _ex form (no stream-K over a batch).  L = 0 is a no-op. */
+int spork_gemm_sm100_f16f32_batched(uint32_t L, uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B,
+                                    float* C, int variant, int split_k, void* stream);
+
 /* Allocation-free GEMM.  Has no counterpart in the reference (whose harness
  * allocates freely, gemm/gemm_test.cu:218-226).  For callers that cannot
  * allocate device memory at call time: code living inside an arena that already

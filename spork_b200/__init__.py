@@ -24,6 +24,7 @@ from .api import (  # noqa: F401
     lib,
     library_path,
     matmul_sm100,
+    matmul_sm100_batched,
     matmul_sm100_htod,
     matmul_sm100_supports,
     matmul_sm100_tf32,

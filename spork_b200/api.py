@@ -65,6 +65,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_tf32f32.restype = i32
         L.spork_gemm_sm100_f16f32_ex.argtypes = [u32, u32, u32, vp, vp, vp, i32, i32, i32, i32, vp]
         L.spork_gemm_sm100_f16f32_ex.restype = i32
+        L.spork_gemm_sm100_f16f32_batched.argtypes = [u32, u32, u32, u32, vp, vp, vp, i32, i32, vp]
+        L.spork_gemm_sm100_f16f32_batched.restype = i32
         L.spork_gemm_sm100_f16f32_static.argtypes = [u32, u32, u32, vp, vp, vp, i32, vp]
         L.spork_gemm_sm100_f16f32_static.restype = i32
         L.spork_selftest_bounded_wait.argtypes = [u32, vp]
@@ -163,6 +165,30 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
             bn = block_n if block_n is not None else (variant or (64 if N <= 64 else 128 if N <= 128 else 256))
             rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cta_group or 2, split_k, max_ctas, sp)
     _check(rc, "spork_gemm_sm100_f16f32")
+    return c
+
+
+def matmul_sm100_batched(a, b, c=None, *, variant: int = 0, split_k: int = 1, stream=None):
+    """c[L,M,N] (fp32) = a[L,M,K] (fp16) @ b[L,N,K]^T (fp16), one launch for the whole batch.
+
+    The batch dimension of the reference's generated entry points (xgemm_Sm90.py:45-48).
+    """
+    import torch
+
+    L, M, K = a.shape
+    L2, N, K2 = b.shape
+    if K != K2 or L != L2:
+        raise ValueError(f"shapes do not match: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if c is None:
+        c = torch.empty((L, M, N), dtype=torch.float32, device=a.device)
+    if tuple(c.shape) != (L, M, N):
+        raise ValueError(f"c must be {(L, M, N)}, got {tuple(c.shape)}")
+    pa = _dev_ptr(a, torch.float16, "a")
+    pb = _dev_ptr(b, torch.float16, "b")
+    pc = _dev_ptr(c, torch.float32, "c")
+    with torch.cuda.device(a.device):
+        rc = lib().spork_gemm_sm100_f16f32_batched(L, M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
+    _check(rc, "spork_gemm_sm100_f16f32_batched")
     return c
 
 

@@ -89,6 +89,7 @@ struct Params {
     uint32_t M, N, K;
     uint32_t tiles_m, tiles_n;   // output tiles (tile = kBlockM*CG x BLOCK_N)
     uint32_t split_k;            // >= 1
+    uint32_t batches;            // >= 1: independent problems A[l] * B[l]^T -> C[l], contiguous in memory
     uint32_t kb_per_split;       // K blocks per split
     uint32_t num_kb;             // ceil(K / kBlockK)
     uint32_t use_tma_store;      // 0: guarded scalar stores (N % 4 != 0)
@@ -117,7 +118,7 @@ struct Barriers {
 };
 
 struct WorkItem {
-    uint32_t m_tile, n_tile, kb_begin, kb_end, split;
+    uint32_t m_tile, n_tile, kb_begin, kb_end, split, batch;
     bool reduce;  // the partial tile is added into C instead of stored
 };
 
@@ -140,7 +141,7 @@ __host__ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t
 __host__ __device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
 {
     if (p.sk_tiles == 0) {
-        const uint32_t items = p.tiles_m * p.tiles_n * p.split_k;
+        const uint32_t items = p.tiles_m * p.tiles_n * p.split_k * p.batches;
         return items > g ? (items - g - 1) / G + 1 : 0;
     }
     const uint32_t n1 = p.dp_tiles / G;  // dp_tiles is a multiple of G
@@ -158,7 +159,9 @@ __host__ __device__ __forceinline__ WorkItem group_item(const Params& p, uint32_
     if (p.sk_tiles == 0) {
         const uint32_t item = g + i * G;
         const uint32_t tiles = p.tiles_m * p.tiles_n;
-        w.split = item / tiles;
+        const uint32_t q = item / tiles;   // (batch, split), split fastest
+        w.batch = q / p.split_k;
+        w.split = q % p.split_k;
         decode_tile(p, item % tiles, w);
         w.kb_begin = w.split * p.kb_per_split;
         const uint32_t e = w.kb_begin + p.kb_per_split;
@@ -167,6 +170,7 @@ __host__ __device__ __forceinline__ WorkItem group_item(const Params& p, uint32_
         return w;
     }
     w.split = 0;
+    w.batch = 0;   // stream-K is never planned for a batch
     const uint32_t n1 = p.dp_tiles / G;
     if (i < n1) {
         decode_tile(p, g + i * G, w);
@@ -291,8 +295,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                         for (int at = 0; at < KATOMS; ++at) {
                             const int32_t x = (int32_t)((kb * KATOMS + at) * kElemsK);
-                            tma_load_2d_hint(sa + at * Cfg::kAtomABytes, &tmap_a, full, x, a_row, pol_a);
-                            tma_load_2d_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, full, x, b_row, pol_b);
+                            if (p.batches > 1) {   // the maps are 3-D then
+                                tma_load_3d_hint(sa + at * Cfg::kAtomABytes, &tmap_a, full, x, a_row, (int32_t)w.batch,
+                                                 pol_a);
+                                tma_load_3d_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, full, x, b_row, (int32_t)w.batch,
+                                                 pol_b);
+                            } else {
+                                tma_load_2d_hint(sa + at * Cfg::kAtomABytes, &tmap_a, full, x, a_row, pol_a);
+                                tma_load_2d_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, full, x, b_row, pol_b);
+                            }
                         }
                     } else {
                         // Both CTAs' bytes complete on the leader's barrier.
@@ -303,8 +314,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                         for (int at = 0; at < KATOMS; ++at) {
                             const int32_t x = (int32_t)((kb * KATOMS + at) * kElemsK);
-                            tma_load_2d_pair_hint(sa + at * Cfg::kAtomABytes, &tmap_a, leader_full, x, a_row, pol_a);
-                            tma_load_2d_pair_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, leader_full, x, b_row, pol_b);
+                            if (p.batches > 1) {
+                                tma_load_3d_pair_hint(sa + at * Cfg::kAtomABytes, &tmap_a, leader_full, x, a_row,
+                                                      (int32_t)w.batch, pol_a);
+                                tma_load_3d_pair_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, leader_full, x, b_row,
+                                                      (int32_t)w.batch, pol_b);
+                            } else {
+                                tma_load_2d_pair_hint(sa + at * Cfg::kAtomABytes, &tmap_a, leader_full, x, a_row, pol_a);
+                                tma_load_2d_pair_hint(sb + at * Cfg::kAtomBBytes, &tmap_b, leader_full, x, b_row, pol_b);
+                            }
                         }
                     }
                     ++issued;
@@ -429,7 +447,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     // straight from registers: every thread writes the 128 contiguous bytes of its row
                     const uint32_t row = row0 + lane;
                     if (row < p.M && col + 32 <= p.N) {
-                        float4* dst = reinterpret_cast<float4*>(p.C + (size_t)row * p.N + col);
+                        float4* dst = reinterpret_cast<float4*>(p.C + ((size_t)w.batch * p.M + row) * p.N + col);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
@@ -459,6 +477,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (lane == 0) {
                         if (kWorkspace) {
                             tma_store_3d(&tmap_c, slab, (int32_t)col, (int32_t)row0, (int32_t)w.split);
+                        } else if (p.batches > 1) {
+                            if (w.reduce) {
+                                tma_reduce_add_3d(&tmap_c, slab, (int32_t)col, (int32_t)row0, (int32_t)w.batch);
+                            } else {
+                                tma_store_3d(&tmap_c, slab, (int32_t)col, (int32_t)row0, (int32_t)w.batch);
+                            }
                         } else if (w.reduce) {
                             tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
                         } else {
@@ -469,7 +493,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 } else {
                     const uint32_t row = row0 + lane;
                     if (row < p.M) {
-                        float* dst = p.C + (size_t)row * p.N + col;
+                        float* dst = p.C + ((size_t)w.batch * p.M + row) * p.N + col;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             if (col + j < p.N) {
@@ -572,12 +596,35 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
+// 3-D map over `batches` such matrices stored one after the other; a box never spans two of them, so
+// ragged rows are zero-filled (loads) or clipped (stores) per matrix.
+static int make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                        uint64_t batches, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        return SPORK_ERR_DRIVER;
+    }
+    const cuuint64_t dims[3] = {cols, rows, batches};
+    const cuuint64_t strides[2] = {cols * elem_bytes, rows * cols * elem_bytes};
+    const cuuint32_t box[3] = {box_cols, box_rows, 1};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    const CUresult r = fn(map, dtype, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
+}
+
 // Host-side launch plan: tile grid, K split, number of CTA groups and the stream-K partition.  Pure
 // arithmetic (no CUDA call), shared by the launch paths and by spork_gemm_sm100_plan.
 static void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m,
                         uint32_t block_n, uint32_t cta_group, uint32_t elems_k, uint32_t split_k, bool stream_k,
-                        int max_ctas, int sm_count)
+                        int max_ctas, int sm_count, uint32_t batches = 1)
 {
+    p.batches = batches < 1 ? 1 : batches;
+    if (p.batches > 1) {
+        stream_k = false;
+    }
     p.M = M;
     p.N = N;
     p.K = K;
@@ -597,7 +644,7 @@ static void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uin
     p.sk_tiles = 0;
     p.sk_share = 0;
     p.sk_extra = 0;
-    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k;
+    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k * p.batches;
     groups = (uint32_t)(sm_count / (int)cta_group);
     if (max_ctas > 0 && (uint32_t)max_ctas / cta_group < groups) {
         groups = (uint32_t)max_ctas / cta_group;
@@ -631,7 +678,7 @@ static Tuning g_tuning;
 
 template <int CG, int BLOCK_N, bool kTf32 = false, int KATOMS = 1>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
-                  int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false)
+                  int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false, uint32_t batches = 1)
 {
     using Cfg = Config<CG, BLOCK_N, KATOMS>;
     auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS>;
@@ -652,7 +699,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     Params p{};
     uint32_t groups = 1;
     plan_launch(p, groups, M, N, K, Cfg::kUmmaM, BLOCK_N, CG, kElemsK * KATOMS, split_k, stream_k, max_ctas,
-                dev.sm_count);
+                dev.sm_count, batches);
     p.C = C;
     p.status = dev.status_word;
     const Tuning tune = g_tuning;
@@ -663,16 +710,20 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     p.experiment = (uint32_t)tune.experiment;
 
     CUtensorMap tmap_a, tmap_b, tmap_c;
-    int rc = make_tmap_2d(&tmap_a, kOperandType, kOperandBytes, A, M, K, kBlockM, kElemsK);
+    int rc = p.batches > 1 ? make_tmap_3d(&tmap_a, kOperandType, kOperandBytes, A, p.batches, M, K, kBlockM, kElemsK)
+                           : make_tmap_2d(&tmap_a, kOperandType, kOperandBytes, A, M, K, kBlockM, kElemsK);
     if (rc) {
         return rc;
     }
-    rc = make_tmap_2d(&tmap_b, kOperandType, kOperandBytes, B, N, K, Cfg::kBRows, kElemsK);
+    rc = p.batches > 1 ? make_tmap_3d(&tmap_b, kOperandType, kOperandBytes, B, p.batches, N, K, Cfg::kBRows, kElemsK)
+                       : make_tmap_2d(&tmap_b, kOperandType, kOperandBytes, B, N, K, Cfg::kBRows, kElemsK);
     if (rc) {
         return rc;
     }
     if (p.use_tma_store) {
-        rc = make_tmap_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, M, N, 32, kEpiCols);
+        rc = p.batches > 1
+                 ? make_tmap_3d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, p.batches, M, N, 32, kEpiCols)
+                 : make_tmap_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, M, N, 32, kEpiCols);
         if (rc) {
             return rc;
         }
@@ -681,7 +732,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     }
 
     if (p.split_k > 1) {
-        const cudaError_t e = cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N, stream);
+        const cudaError_t e = cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N * p.batches, stream);
         if (e != cudaSuccess) {
             return (int)e;
         }
@@ -717,13 +768,17 @@ static bool aligned16(const void* p)
 }
 
 static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int block_n,
-                    int cta_group, int split_k, int max_ctas, cudaStream_t stream, bool tf32 = false)
+                    int cta_group, int split_k, int max_ctas, cudaStream_t stream, bool tf32 = false,
+                    uint32_t batches = 1)
 {
     if (tf32 ? (K % 4 != 0) : !spork_gemm_sm100_supports(M, N, K)) {
         return SPORK_ERR_UNSUPPORTED_SHAPE;
     }
-    if (M == 0 || N == 0) {
+    if (M == 0 || N == 0 || batches == 0) {
         return 0;
+    }
+    if (batches > 1 && (split_k == -1 || (uint64_t)batches * ((M + 127) / 128) * ((N + 63) / 64) > 0x3FFFFFFFull)) {
+        return SPORK_ERR_BAD_ARGUMENT;  // no stream-K over a batch; the item index is 32 bits wide
     }
     if (!A || !B || !C || !aligned16(A) || !aligned16(B) || !aligned16(C)) {
         // K == 0 with null A/B is still an error only if they would be read; be strict and simple.
@@ -735,7 +790,7 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
         return SPORK_ERR_BAD_ARGUMENT;
     }
     if (K == 0) {
-        return (int)cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N, stream);
+        return (int)cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N * batches, stream);
     }
     DeviceState* dev = nullptr;
     const int rc = current_device_state(&dev);
@@ -746,30 +801,31 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
     // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
     // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.
-    const uint64_t out_tiles = (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n);
+    const uint64_t out_tiles =
+        (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
     const bool wide_k = !tf32 && cta_group == 2 &&
                         (g_tuning.k_atoms == 2 || (g_tuning.k_atoms == 0 && block_n <= 128 &&
                                                    out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
     if (wide_k) {
         switch (block_n) {
-        case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
-        case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
-        case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
 #define SPORK_GEMM_CASE(CG_, BN_)                                                               \
     if (cta_group == CG_ && block_n == BN_) {                                                   \
-        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);        \
+        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);        \
     }
     if (tf32) {
         if (cta_group != 2) {
             return SPORK_ERR_BAD_ARGUMENT;
         }
         switch (block_n) {
-        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
-        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
-        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k);
+        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
@@ -836,6 +892,7 @@ static int launch_static(uint32_t M, uint32_t N, uint32_t K, const void* A, cons
         return (int)attr_err[ordinal];
     }
     Params p{};
+    p.batches = 1;
     p.M = M;
     p.N = N;
     p.K = K;
@@ -1138,6 +1195,20 @@ extern "C" int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, cons
     }
     return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, 2, split_k, 0, static_cast<cudaStream_t>(stream),
                                        true);
+}
+
+extern "C" int spork_gemm_sm100_f16f32_batched(uint32_t L, uint32_t M, uint32_t N, uint32_t K, const void* A,
+                                               const void* B, float* C, int variant, int split_k, void* stream)
+{
+    int block_n = variant;
+    if (variant == 0) {
+        block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
+    }
+    if ((block_n != 64 && block_n != 128 && block_n != 256) || split_k < 1) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, SPORK_DEFAULT_CTA_GROUP, split_k, 0,
+                                       static_cast<cudaStream_t>(stream), false, L);
 }
 
 extern "C" int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,

@@ -263,6 +263,29 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// 3-D forms of the hinted loads: z selects the matrix of a batch.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int32_t x,
+                                                 int32_t y, int32_t z, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t cluster_bar,
+                                                      int32_t x, int32_t y, int32_t z, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        :
+        : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+}
+
 // 2-D tile store, shared -> global (elements outside the tensor are clipped).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int32_t x, int32_t y)
 {
@@ -285,6 +308,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sm
                                              int32_t z)
 {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, uint32_t smem_src, int32_t x, int32_t y,
+                                                  int32_t z)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
                  :
                  : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_src), "r"(x), "r"(y), "r"(z)
                  : "memory");

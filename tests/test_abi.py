@@ -44,6 +44,10 @@ def test_supports_and_argument_errors_need_no_gpu(sp):
     # unsupported shape and bad variant are rejected before any CUDA call
     assert L.spork_gemm_sm100_f16f32(128, 128, 12, None, None, None, 0, None) == 10002
     assert L.spork_gemm_sm100_f16f32(128, 128, 16, None, None, None, 96, None) == 10001
+    # the batched form checks its arguments the same way
+    assert L.spork_gemm_sm100_f16f32_batched(4, 128, 128, 12, None, None, None, 0, 1, None) == 10002
+    assert L.spork_gemm_sm100_f16f32_batched(4, 128, 128, 16, None, None, None, 0, 0, None) == 10001
+    assert L.spork_gemm_sm100_f16f32_batched(0, 128, 128, 16, None, None, None, 0, 1, None) == 0  # empty batch
     assert "sm_100a" in sp.version()
 
 
