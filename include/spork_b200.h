@@ -46,8 +46,10 @@ extern "C" {
  * (gemm/gemm_sm80.h:6) / the asserts of gemm/gemm_sm90.cu:1269-1276. */
 int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K);
 
-/* Launch.  variant: 0 = choose, 64 / 128 / 256 = width of the output tile
- * along N (the n64/n128/n256 variants of xgemm_Sm90_n{64,128,256}.py).
+/* Launch.  variant: 0 = choose (width from N, CTA pairs; single CTAs with
+ * tiles at most 128 wide for small latency-bound problems), 64 / 128 / 256 =
+ * width of the output tile along N, taken literally, on CTA pairs (the
+ * n64/n128/n256 variants of xgemm_Sm90_n{64,128,256}.py).
  * Replaces matmul_sm90(t, gemm_sm90_k_mode::output_stationary, stream)
  * (gemm/gemm_sm90.cu:1344-1360). */
 int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int variant,
