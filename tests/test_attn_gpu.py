@@ -207,3 +207,46 @@ def test_attention_argument_errors(sp, cuda):
     assert sp.lib().spork_attn_sm100_supports(16, 4096, 128) == 1
     assert sp.lib().spork_attn_sm100_supports(16, 4096, 80) == 0
     sp.status()
+
+
+def _ramp_inputs(cuda, BH, S, D, per_key, noise_seed):
+    """Scores that move steadily along the keys: q_i = (a, noise...), k_j = (per_key * j, noise...), so that
+    s_ij = a * per_key * j + noise.  The row maximum keeps moving from block to block, which drives the
+    kernel through the rescaling of its accumulators (or, falling, lets every later block underflow)."""
+    import torch
+
+    g = torch.Generator(device="cpu").manual_seed(noise_seed)
+    q = torch.randn((BH, S, D), generator=g) * 0.25
+    k = torch.randn((BH, S, D), generator=g) * 0.25
+    v = torch.randn((BH, S, D), generator=g)
+    q[:, :, 0] = 4.0
+    k[:, :, 0] = per_key * torch.arange(S, dtype=torch.float32)[None, :]
+    return (t.to(torch.float16).to(cuda).contiguous() for t in (q, k, v))
+
+
+# per-key steps of the score ramp: one 128-key block moves the scaled, log2 score by
+# 4 * step * 128 * scale * log2(e); with scale = 1/sqrt(128) that is 65 * step: 0.05 -> 3 per block (below the
+# lazy-rescale threshold of 8 most of the time), 0.25 -> 16 per block, 1.0 -> 65 per block (every block
+# rescales), negative: scores fall away from the first block's maximum.
+@pytest.mark.parametrize("per_key", [0.05, 0.25, 1.0, 3.0, -0.25, -2.0])
+@pytest.mark.parametrize("causal", [False, True])
+def test_moving_row_maximum(sp, orc, cuda, per_key, causal):
+    BH, S, D = 2, 1024, 128
+    q, k, v = _ramp_inputs(cuda, BH, S, D, per_key, 7)
+    o = sp.attn_fwd(q, k, v, causal=causal)
+    sp.status()
+    f = orc.attn_causal_f16 if causal else orc.attn_f16
+    _, ref = f(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    ok, worst = _close(o.cpu().numpy(), ref)
+    assert ok, f"max abs error {worst}"
+
+
+def test_moving_row_maximum_d64_ragged(sp, orc, cuda):
+    BH, S, D = 3, 700, 64
+    for per_key in (0.2, 0.7, -0.4):
+        q, k, v = _ramp_inputs(cuda, BH, S, D, per_key, 11)
+        o = sp.attn_fwd(q, k, v)
+        sp.status()
+        _, ref = orc.attn_f16(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+        ok, worst = _close(o.cpu().numpy(), ref)
+        assert ok, f"per_key {per_key}: max abs error {worst}"
