@@ -1,5 +1,5 @@
 // Attention forward for sm_100a (B200): O = softmax(Q K^T * scale) V per head,
-// fp16 in, fp32 softmax, fp16 out, non-causal.
+// fp16 or bfloat16 in and out, fp32 softmax, optionally with a causal mask.
 //
 // Takes the place of the reference's attention launch entry
 // (launch_tk_4090_fwd_kernel / htod_f32_tk_4090_fwd, tk_4090_fwd.hpp:5-7; the
