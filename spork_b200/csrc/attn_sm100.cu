@@ -133,6 +133,13 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
     return r;
 }
 
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 __device__ __forceinline__ float fma_sat(float a, float b, float c)
 {
     float r;
@@ -147,8 +154,9 @@ __device__ __forceinline__ float fma_sat(float a, float b, float c)
 // the 1.5*2^23 trick, the fraction goes through a cubic (relative error 7e-5, well under the rounding of P
 // to 16 bits) and round(x) is added into the exponent field. ks = sl2 / 64, cs = (neg_m + kPolyLo) / 64.
 constexpr float kPolyLo = 56.0f;
-// How many of every eight pairs of exponentials take that route. Measured at B*H = 256, S = 4096:
-// 0 -> 1249, 2 -> 1259, 3 -> 1265, 4 -> 1241 TFLOP/s (D = 128).
+// How many of every eight pairs of exponentials take that route. Measured at B*H = 256, S = 4096, D = 128,
+// interleaved runs on a part warmed into its power cap: 0 -> 1099, 1 -> 1145, 2 -> 1163, 3 -> 1173,
+// 4 -> 1069 TFLOP/s (cold: 1264, 1281, 1173, 1193, 1112).
 constexpr int kPolyPairs = 3;
 __device__ __forceinline__ void ex2_poly2(float s0, float s1, float ks, float cs, float& p0, float& p1)
 {
@@ -508,7 +516,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             const float neg_m = -m_ref * sl2;
             const float ks = sl2 * (1.0f / 64.0f);
             const float cs = (neg_m + kPolyLo) * (1.0f / 64.0f);
-            float l_blk0 = 0.0f, l_blk1 = 0.0f;
+            // packed forms where both elements of a pair take the same step: half the issue slots
+            const uint64_t sl2_2 = pack2(sl2, sl2);
+            const uint64_t neg_m2 = pack2(neg_m, neg_m);
+            uint64_t l_blk2 = pack2(0.0f, 0.0f);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t packed[32];
@@ -520,11 +531,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     if ((i & 7) < kPolyPairs) {
                         ex2_poly2(s0, s1, ks, cs, p0, p1);
                     } else {
-                        p0 = ex2_approx(fmaf(s0, sl2, neg_m));
-                        p1 = ex2_approx(fmaf(s1, sl2, neg_m));
+                        float x0, x1;
+                        unpack2(fma2(pack2(s0, s1), sl2_2, neg_m2), x0, x1);
+                        p0 = ex2_approx(x0);
+                        p1 = ex2_approx(x1);
                     }
-                    l_blk0 += p0;
-                    l_blk1 += p1;
+                    l_blk2 = add2(l_blk2, pack2(p0, p1));
                     packed[i] = pack_half2<kBf16>(p0, p1);
                 }
                 tmem_st_32x32b_x32(tmem_s + half * 32, packed);
@@ -533,6 +545,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tcgen05_fence_before();
                 mbar_arrive(smem_u32(&bars->p_ready[w][half]));
             }
+            float l_blk0, l_blk1;
+            unpack2(l_blk2, l_blk0, l_blk1);
             l_run = l_run * alpha + (l_blk0 + l_blk1);
         }
         // ---- epilogue: O_w / l -> fp16 -> global
