@@ -430,7 +430,7 @@ def main():
 
         oracle.use_all_cores()
         tf, dt, a_rows, b_host = cpu_sample(oracle, 64)
-        rows = int(max(64, min(M_PER_RANK, (12.0 / max(dt, 1e-6)) * 64)))  # about 12 s of CPU work
+        rows = int(max(64, min(M_PER_RANK, (30.0 / max(dt, 1e-6)) * 64)))  # 10-15 s of CPU work (the 64-row probe runs slower per row)
         rows -= rows % 64
         tf, dt, _, _ = cpu_sample(oracle, rows, None, b_host)
         cpu_baseline = {"value": tf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
