@@ -124,8 +124,9 @@ int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
 
 /* Process-wide tuning of later launches (benchmark sweeps; the defaults are the
  * measured best).  stages: shared-memory ring depth, 0 = as deep as fits;
- * group_m: m-tiles per raster group, 0 = default; l2_hints: bit 0 = A loads
- * evict-last, bit 1 = B loads evict-last, bit 2 = B loads evict-first;
+ * group_m: m-tiles per raster group, 0 = default; l2_hints, low four bits: 0 =
+ * default (A and B loads evict-last), bit 0 = A loads evict-last, bit 1 = B loads
+ * evict-last, bit 2 = B loads evict-first, 8 = no hints at all;
  * backoff_ns: sleep between polls of the long waits, 0 = spin.  Bits 8..9 of
  * l2_hints: 128-byte column blocks per ring stage (1 or 2; 0 = chosen per shape:
  * 2 for skinny HBM-bound problems).  Bits 4..6 of
