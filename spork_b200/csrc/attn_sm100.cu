@@ -11,7 +11,7 @@
 //   warps 0-3  softmax of query tile 0 (one thread = one query row)
 //   warps 4-7  softmax of query tile 1
 //   warp  8    TMA producer (Q tiles once, then K_j, V_j through a ring)
-//   warp  9    tcgen05.mma issuer (one thread) and TMEM owner
+//   warp  9    tcgen05.mma issuer (the whole warp runs the control flow, an elected lane issues) and TMEM owner
 //   warps 10-11 idle: they complete the third warpgroup, so that whole warpgroups can trade
 //              registers (setmaxnreg): 216 per softmax thread, 72 for the rest
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
@@ -31,7 +31,8 @@
 // The two query tiles alternate, so the tensor core works on one tile while the
 // other tile's softmax runs.  Keys past the end of a ragged sequence are masked
 // to -inf; rows past the end are computed on zero-filled queries and not stored.
-// Every wait is bounded (see ptx_sm100.cuh).
+// Every wait on a barrier is bounded (see ptx_sm100.cuh); the one wait that is not, setmaxnreg's for free
+// registers, cannot block because the trade fits the launch allocation (static_assert below).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
