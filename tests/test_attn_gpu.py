@@ -250,3 +250,32 @@ def test_moving_row_maximum_d64_ragged(sp, orc, cuda):
         _, ref = orc.attn_f16(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
         ok, worst = _close(o.cpu().numpy(), ref)
         assert ok, f"per_key {per_key}: max abs error {worst}"
+
+
+def test_the_reference_script_at_its_own_size(sp, cuda):
+    """The flow of the reference's torch_attn.py at its own size and seeds (N = 2560, d = 64, inputs
+    rand(seed)^3.6 with seeds 101 / 237 / 280, torch_attn.py:4-7,26-29): the math of simple_attn and torch's
+    scaled_dot_product_attention on the CPU against the host-pointer entry point the script would load."""
+    import math
+
+    import torch
+
+    N, d = 2560, 64
+
+    def make(seed):
+        g = torch.Generator().manual_seed(seed)
+        return torch.pow(torch.rand((N, d), dtype=torch.float32, generator=g), 3.6)
+
+    q, k, v = make(101), make(237), make(280)
+    s = (q @ k.t()) * (1.0 / math.sqrt(d))
+    simple_o = torch.softmax(s, dim=-1) @ v
+    torch_o = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    o = torch.empty((N, d), dtype=torch.float32)
+    f32p = ctypes.POINTER(ctypes.c_float)
+    as_ptr = lambda t: ctypes.cast(t.data_ptr(), f32p)  # noqa: E731
+    sp.lib().htod_f32_attn_sm100_fwd(N, d, as_ptr(q), as_ptr(k), as_ptr(v), as_ptr(o))
+    sp.status()
+    # inputs are rounded to fp16 on the way in and the result on the way out: the same bound as elsewhere
+    for ref in (simple_o, torch_o):
+        ok, worst = _close(o.numpy(), ref.numpy())
+        assert ok, f"max abs error {worst}"
