@@ -123,7 +123,8 @@ struct WorkItem {
 };
 
 // Grouped raster (the superblock idea of gemm/gemm_sm90.cu:318-345): work items
-// that run at the same time cover kGroupM m-tiles by a run of n-tiles.
+// that run at the same time cover kGroupM m-tiles by a run of n-tiles; the groups
+// alternate their direction along n.
 __host__ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkItem& w)
 {
     const uint32_t group_size = p.group_m * p.tiles_n;
@@ -133,6 +134,11 @@ __host__ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t
     const uint32_t r = t % group_size;
     w.m_tile = first_m + r % gm;
     w.n_tile = r / gm;
+    // every other group walks the n-tiles backwards: the B strips the previous group touched last are the
+    // first to be used again while they are still in L2 (+0.5 % at 8192^3 with the part at its power cap)
+    if (g & 1u) {
+        w.n_tile = p.tiles_n - 1u - w.n_tile;
+    }
 }
 
 // Work of CTA group `g` of `G`.  Without stream-K: items g, g+G, ... of the (split, tile) list.  With
