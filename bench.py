@@ -33,7 +33,7 @@ FLOPS_PER_STEP = 2.0 * M_PER_RANK * N_DIM * K_DIM
 # algorithmic bytes of one launch: A + B read once, C written once
 BYTES_PER_STEP = 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM + 4 * M_PER_RANK * N_DIM
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel at this size (see profiles/)
-NCU_TRAFFIC_BYTES = 1.096e9 + 0.2534e9
+NCU_TRAFFIC_BYTES = 1.051e9 + 0.2535e9
 
 
 def measured_peaks():
