@@ -32,6 +32,7 @@ enum class gemm_sm100_k_mode
     output_stationary,
     split_k_outer,
     stream_k,  // the last partial wave of tiles is cut along K over all CTA pairs (gemm_sm90_k_mode::stream_k_*)
+    automatic, // output_stationary, or split_k_outer with a split count chosen to fill the waves (few tiles, long K)
 };
 
 // The kernel takes the harness's hot layout only: A row-major, B stored N x K,
@@ -51,10 +52,11 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
         return SPORK_ERR_UNSUPPORTED_SHAPE;
     }
     int rc;
-    if ((k_mode == gemm_sm100_k_mode::split_k_outer && split_k > 1) || k_mode == gemm_sm100_k_mode::stream_k) {
+    if ((k_mode == gemm_sm100_k_mode::split_k_outer && split_k > 1) || k_mode == gemm_sm100_k_mode::stream_k ||
+        k_mode == gemm_sm100_k_mode::automatic) {
         const int block_n = variant ? variant : (t.N <= 64 ? 64 : (t.N <= 128 ? 128 : 256));
-        rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, 2,
-                                        k_mode == gemm_sm100_k_mode::stream_k ? -1 : split_k, 0, stream);
+        const int split = k_mode == gemm_sm100_k_mode::stream_k ? -1 : (k_mode == gemm_sm100_k_mode::automatic ? 0 : split_k);
+        rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, 2, split, 0, stream);
     } else {
         rc = spork_gemm_sm100_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, variant, stream);
     }

@@ -68,7 +68,10 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
  *   block_n   64 / 128 / 256   output-tile width
  *   cta_group 1 = one CTA per tile (128 x block_n),
  *             2 = a CTA pair per tile (256 x block_n, tcgen05 cta_group::2)
- *   split_k   >= 1: K is cut into split_k ranges whose partial products are
+ *   split_k   0: chosen by the library (1 unless the problem has fewer 256-wide
+ *             output tiles than CTA pairs and a long K; then the count that
+ *             fills the waves best, see spork_gemm_sm100_plan);
+ *             >= 1: K is cut into split_k ranges whose partial products are
  *             added into C with TMA reduce-add (C is zeroed first); the
  *             counterpart of gemm_sm90_k_mode::split_k_outer
  *             (gemm/gemm_sm90.h:8, gemm/gemm_sm90.cu:1096-1114).
@@ -89,7 +92,7 @@ int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A
  * column-major C swaps the operands, as for the single product.  The kernel is
  * the same persistent kernel: the batch index is one more coordinate of the tile
  * scheduler and of 3-D tensor maps, so ragged M and N are zero-filled and
- * clipped per matrix.  `variant` as for spork_gemm_sm100_f16f32; split_k >= 1 as
+ * clipped per matrix.  `variant` as for spork_gemm_sm100_f16f32; split_k >= 0 as
  * for the _ex form (no stream-K over a batch).  L = 0 is a no-op. */
 int spork_gemm_sm100_f16f32_batched(uint32_t L, uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B,
                                     float* C, int variant, int split_k, void* stream);

@@ -621,6 +621,43 @@ static int make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
+// split_k = 0 ("choose"): a problem with fewer output tiles than CTA groups and a long K leaves SMs idle;
+// cutting K into s ranges turns it into tiles * s work items.  Pick the s (1..16, at least 8 K blocks per
+// range) with the smallest modelled time: waves(s) * (K blocks per range * cycles per block + epilogue),
+// where a reduce-add epilogue is dearer than a store.  Only for 256-wide tiles: narrower ones are chosen
+// for problems that are bound by memory, where this model does not hold.  Pure arithmetic.
+static uint32_t choose_split(uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m, uint32_t block_n, uint32_t cta_group,
+                             uint32_t elems_k, int max_ctas, int sm_count, uint32_t batches)
+{
+    const uint64_t tiles = (uint64_t)((M + tile_m - 1) / tile_m) * ((N + block_n - 1) / block_n) * (batches ? batches : 1);
+    const uint32_t num_kb = (K + elems_k - 1) / elems_k;
+    uint32_t groups = (uint32_t)(sm_count / (int)cta_group);
+    if (max_ctas > 0 && (uint32_t)max_ctas / cta_group < groups) {
+        groups = (uint32_t)max_ctas / cta_group;
+    }
+    if (block_n != 256 || groups == 0 || tiles >= groups || num_kb < 16) {
+        return 1;
+    }
+    const uint64_t cycles_per_kb = 512, epilogue_store = 4000, epilogue_reduce = 6000;
+    uint32_t best = 1;
+    uint64_t best_time = (uint64_t)num_kb * cycles_per_kb + epilogue_store;  // one wave, s = 1
+    for (uint32_t s = 2; s <= 16; ++s) {
+        const uint32_t kb_per = (num_kb + s - 1) / s;
+        if (kb_per < 8) {
+            break;
+        }
+        const uint32_t splits = (num_kb + kb_per - 1) / kb_per;  // no empty ranges
+        const uint64_t items = tiles * splits;
+        const uint64_t waves = (items + groups - 1) / groups;
+        const uint64_t t = waves * ((uint64_t)kb_per * cycles_per_kb + epilogue_reduce);
+        if (t < best_time) {
+            best_time = t;
+            best = splits;
+        }
+    }
+    return best;
+}
+
 // Host-side launch plan: tile grid, K split, number of CTA groups and the stream-K partition.  Pure
 // arithmetic (no CUDA call), shared by the launch paths and by spork_gemm_sm100_plan.
 static void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m,
@@ -806,7 +843,7 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
             return SPORK_ERR_BAD_ARGUMENT;
         }
     }
-    if ((split_k < 1 && split_k != -1) || max_ctas < 0) {
+    if (split_k < -1 || max_ctas < 0) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     if (K == 0) {
@@ -829,6 +866,10 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
             cta_group = 1;
             block_n = block_n > 128 ? 128 : block_n;
         }
+    }
+    if (split_k == 0) {
+        split_k = (int)choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n, (uint32_t)cta_group,
+                                    tf32 ? 32u : 64u, max_ctas, dev->sm_count, batches);
     }
     const bool stream_k = split_k == -1;
     const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
@@ -1116,8 +1157,12 @@ static bool plan_from_args(spork::gemm_sm100::Params& p, uint32_t& groups, uint3
                            int block_n, int cta_group, int split_k, int max_ctas, int sm_count, int tf32)
 {
     if ((block_n != 64 && block_n != 128 && block_n != 256) || (cta_group != 1 && cta_group != 2) ||
-        (split_k < 1 && split_k != -1) || max_ctas < 0 || sm_count < cta_group) {
+        split_k < -1 || max_ctas < 0 || sm_count < cta_group) {
         return false;
+    }
+    if (split_k == 0) {
+        split_k = (int)spork::gemm_sm100::choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n,
+                                                       (uint32_t)cta_group, tf32 ? 32u : 64u, max_ctas, sm_count, 1);
     }
     spork::gemm_sm100::plan_launch(p, groups, M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n,
                                    (uint32_t)cta_group, tf32 ? 32u : 64u, split_k == -1 ? 1u : (uint32_t)split_k,
@@ -1240,7 +1285,7 @@ extern "C" int spork_gemm_sm100_f16f32_batched(uint32_t L, uint32_t M, uint32_t 
     if (variant == 0) {
         block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
     }
-    if ((block_n != 64 && block_n != 128 && block_n != 256) || split_k < 1) {
+    if ((block_n != 64 && block_n != 128 && block_n != 256) || split_k < 0) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, variant == 0 ? 0 : SPORK_DEFAULT_CTA_GROUP, split_k,

@@ -31,8 +31,9 @@ enum class AlgorithmCode {
     mine_sm_100_n64,
     mine_sm_100_split_k,
     mine_sm_100_stream_k,
+    mine_sm_100_auto_k,
 };
-constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_stream_k);
+constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_auto_k);
 
 inline uint32_t algorithm_code_bit(AlgorithmCode code) { return 1u << static_cast<uint32_t>(code); }
 
@@ -46,6 +47,7 @@ inline const char* algorithm_name(AlgorithmCode code)
     case AlgorithmCode::mine_sm_100_n64: return "mine_sm_100_n64";
     case AlgorithmCode::mine_sm_100_split_k: return "mine_sm_100 (split k)";
     case AlgorithmCode::mine_sm_100_stream_k: return "mine_sm_100 (stream k)";
+    case AlgorithmCode::mine_sm_100_auto_k: return "mine_sm_100 (automatic k)";
     }
     return "unknown";
 }
@@ -138,6 +140,9 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
                 break;
             case AlgorithmCode::mine_sm_100_stream_k:
                 launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::stream_k);
+                break;
+            case AlgorithmCode::mine_sm_100_auto_k:
+                launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::automatic);
                 break;
             }
             CUDA_OK(cudaEventRecord(test_events[test_i + 1], stream));
@@ -240,6 +245,9 @@ int main(int argc, char** argv)
                 params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_split_k);
             }
             params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_stream_k);
+            if (K >= 4096) {
+                params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_auto_k);
+            }
         }
         auto run = [&](TestDataCode a, TestDataCode b) {
             params.test_data_code_A = a;

@@ -230,8 +230,8 @@ def test_argument_errors_are_returned_not_trapped(sp, cuda):
     assert L.spork_gemm_sm100_f16f32(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 100, None) == 10001
     assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 3, 1, 0,
                                         None) == 10001
-    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 2, 0, 0,
-                                        None) == 10001
+    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 2, -2, 0,
+                                        None) == 10001  # split_k: 0 = choose, -1 = stream-K, nothing below
     with pytest.raises(TypeError):
         sp.matmul_sm100(a.float(), b)
     with pytest.raises(ValueError):
@@ -350,3 +350,14 @@ def test_reference_oracle_kernel_agrees_with_cpu_oracle(orc, cuda):
             torch.cuda.synchronize()
             # TF32 keeps 10 mantissa bits, as many as fp16: the inputs are exact, only summation order differs
             assert orc.ratio_compare(ref, c2.cpu().numpy()) is None
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 16384), (300, 520, 8192), (1536, 2304, 8192)])
+def test_automatic_split_k(sp, orc, cuda, M, N, K):
+    """split_k = 0: the library picks the number of K ranges (few output tiles, long K); the sum is the same
+    product within the headline tolerance."""
+    a, b = _inputs(sp, orc, cuda, M, N, K, sp.DATA_UNIFORM_PM1, sp.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c, split_k=0)
+    sp.status()
+    _check(sp, orc, a, b, c, K)

@@ -49,7 +49,7 @@ def test_split_k_is_normalised(L):
     p = _plan(L, 512, 512, 2048, 128, 2, 3)
     assert p["kb_per_split"] == 11 and p["split_k"] == 3  # 11 + 11 + 10, no empty split
     assert L.spork_gemm_sm100_plan(1, 1, 8, 100, 2, 1, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001
-    assert L.spork_gemm_sm100_plan(1, 1, 8, 128, 2, 0, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001
+    assert L.spork_gemm_sm100_plan(1, 1, 8, 128, 2, -2, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001  # 0 = choose, -1 = stream-K
 
 
 @pytest.mark.parametrize("shape,bn,cg,sk,max_ctas", [
@@ -90,3 +90,27 @@ def test_raster_keeps_concurrent_tiles_compact(L):
     ms = {m for m, _ in firsts}
     ns = {n for _, n in firsts}
     assert ms == set(range(8)) and len(ns) <= 10
+
+
+def test_automatic_split_fills_the_waves(L):
+    """split_k = 0 leaves the count to the library: 1 when the tiles fill the machine or K is short, else the
+    count that makes the best use of the waves (the reference's huge-K shapes, gemm/gemm_main.cpp:111-117)."""
+    assert _plan(L, 8192, 8192, 8192, 256, 2, 0)["split_k"] == 1          # 1024 tiles for 74 CTA pairs
+    assert _plan(L, 512, 512, 512, 256, 2, 0)["split_k"] == 1             # 8 K blocks: too short to cut
+    assert _plan(L, 16384, 64, 8192, 64, 2, 0)["split_k"] == 1            # narrow tiles: bound by memory
+    p = _plan(L, 1536, 2304, 65536, 256, 2, 0)                             # 54 tiles: 4 x 54 = 216 items = 2.92 waves
+    assert p["split_k"] == 4 and p["kb_per_split"] == 256
+    p = _plan(L, 1024, 2816, 49152, 256, 2, 0)                             # 44 tiles: 5 x 44 = 220 items = 2.97 waves
+    assert p["split_k"] == 5
+    p = _plan(L, 512, 512, 16384, 256, 2, 0)                               # 4 tiles: as many ranges as allowed
+    assert p["split_k"] == 16 and p["kb_per_split"] == 16
+    # every K block of every tile is still covered exactly once
+    seen = {}
+    p = _plan(L, 1024, 2816, 49152, 256, 2, 0)
+    for g in range(p["groups"]):
+        for (m, n, k0, k1, reduce) in _items(L, 1024, 2816, 49152, 256, 2, 0, g):
+            assert reduce == 1
+            for kb in range(k0, k1):
+                assert (m, n, kb) not in seen
+                seen[(m, n, kb)] = True
+    assert len(seen) == p["tiles_m"] * p["tiles_n"] * p["num_kb"]
