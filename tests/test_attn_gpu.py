@@ -279,3 +279,24 @@ def test_the_reference_script_at_its_own_size(sp, cuda):
     for ref in (simple_o, torch_o):
         ok, worst = _close(o.numpy(), ref.numpy())
         assert ok, f"max abs error {worst}"
+
+
+def test_headline_size_and_long_sequences(sp, cuda):
+    """The benchmark's own size (B*H = 256, S = 4096, D = 128: every CTA of 28 waves) and a sequence four times
+    as long, through properties and a second implementation, since the CPU oracle would take minutes:
+    V = ones gives O = 1, and sampled heads agree with torch's scaled_dot_product_attention on the GPU."""
+    import torch
+
+    for BH, S, D, heads in ((256, 4096, 128, (0, 100, 255)), (4, 16384, 128, (1, 3)), (8, 8192, 64, (2, 7))):
+        q, k, v = _qkv(sp, cuda, BH, S, D, seed=280)
+        o = sp.attn_fwd(q, k, torch.ones_like(v))
+        sp.status()
+        assert float((o.float() - 1.0).abs().max()) < 2e-3, (BH, S, D)
+        o = sp.attn_fwd(q, k, v)
+        sp.status()
+        for h in heads:
+            ref = torch.nn.functional.scaled_dot_product_attention(q[h:h + 1].float(), k[h:h + 1].float(),
+                                                                   v[h:h + 1].float())
+            ok, worst = _close(o[h:h + 1].cpu().numpy(), ref.cpu().numpy())
+            assert ok, f"{(BH, S, D)} head {h}: max abs error {worst}"
+        del q, k, v, o
