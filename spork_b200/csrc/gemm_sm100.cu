@@ -377,26 +377,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
                     if (elected) {
 #pragma unroll
-                    for (int at = 0; at < KATOMS; ++at) {
-                        const uint64_t desc_a = umma_desc_kmajor_sw128(sa + at * Cfg::kAtomABytes);
-                        const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes + at * Cfg::kAtomBBytes);
+                        for (int at = 0; at < KATOMS; ++at) {
+                            const uint64_t desc_a = umma_desc_kmajor_sw128(sa + at * Cfg::kAtomABytes);
+                            const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes + at * Cfg::kAtomBBytes);
 #pragma unroll
-                        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                            // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the (>>4) address field.
-                            const uint32_t acc = (kb != w.kb_begin || at != 0 || k != 0) ? 1u : 0u;
-                            if (kTf32) {
-                                umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
-                            } else {
-                                umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                                // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the (>>4) address field.
+                                const uint32_t acc = (kb != w.kb_begin || at != 0 || k != 0) ? 1u : 0u;
+                                if (kTf32) {
+                                    umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                                } else {
+                                    umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                                }
                             }
                         }
-                    }
-                    // Free the stage (in both CTAs) once these MMAs have read it.
-                    const uint32_t empty = smem_u32(&bars->empty[stage]);
-                    umma_commit<CG>(empty);
-                    if (CG == 2) {
-                        umma_commit<CG>(map_to_cta(empty, 1));
-                    }
+                        // Free the stage (in both CTAs) once these MMAs have read it.
+                        const uint32_t empty = smem_u32(&bars->empty[stage]);
+                        umma_commit<CG>(empty);
+                        if (CG == 2) {
+                            umma_commit<CG>(map_to_cta(empty, 1));
+                        }
                     }
                     if (++stage == p.stages) {
                         stage = 0;
