@@ -32,8 +32,10 @@ K_DIM = 8192
 FLOPS_PER_STEP = 2.0 * M_PER_RANK * N_DIM * K_DIM
 # algorithmic bytes of one launch: A + B read once, C written once
 BYTES_PER_STEP = 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM + 4 * M_PER_RANK * N_DIM
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel at this size (see profiles/)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at this size, and the
+# committed ncu summary the figure was read from
 NCU_TRAFFIC_BYTES = 1.051e9 + 0.2535e9
+NCU_TRAFFIC_SOURCE = "profiles/gemm_kernel_8192cubed.md"
 
 
 def measured_peaks():
@@ -68,10 +70,17 @@ class ClockSampler:
         self._thread = None
         try:
             import pynvml
+            import torch
 
             pynvml.nvmlInit()
             self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            # The management library numbers the machine's GPUs, CUDA numbers the visible ones: look the
+            # device up by its UUID so that the samples are of the GPU this process computes on.
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except TypeError:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
             self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
         except Exception:
             self._nv = None
@@ -171,7 +180,7 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
     this rank's heads."""
     from spork_b200.sharding import head_slab
 
-    BH_TOTAL, S, D = 256, 4096, 128
+    BH_TOTAL, S, D = args.heads, 4096, args.head_dim
     slab = head_slab(BH_TOTAL, rank, world)
     qkv = []
     for seed in (101, 101 ^ 888, 101 ^ 1776):
@@ -179,8 +188,9 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
         sp.init_test_data(t, sp.DATA_NORMAL, seed, row0=slab.start * S)
         qkv.append(t.view(slab.count, S, D))
     o = torch.empty_like(qkv[0])
+    causal = bool(args.causal)
     for _ in range(args.warmup):
-        sp.attn_fwd(qkv[0], qkv[1], qkv[2], o)
+        sp.attn_fwd(qkv[0], qkv[1], qkv[2], o, causal=causal)
     sp.status()
     events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     torch.cuda.synchronize()
@@ -190,7 +200,7 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
     with ClockSampler(dev.index) as clocks:
         events[0].record()
         for i in range(args.steps):
-            sp.attn_fwd(qkv[0], qkv[1], qkv[2], o)
+            sp.attn_fwd(qkv[0], qkv[1], qkv[2], o, causal=causal)
             events[i + 1].record()
         torch.cuda.synchronize()
     if dist is not None:
@@ -202,21 +212,51 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
     if rank != 0:
         return
     ms_per_step = float(t.item()) / args.steps
-    flops = 4.0 * BH_TOTAL * S * S * D
+    flops = 4.0 * BH_TOTAL * S * S * D * (0.5 if causal else 1.0)
     value = flops / (ms_per_step * 1e-3) / 1e12
     peaks = measured_peaks()
-    print(json.dumps({"metric": "attention forward TFLOP/s (B=16 H=16 S=4096 D=128, fp16, non-causal)", "value": value,
+    print(json.dumps({"metric": f"attention forward TFLOP/s (BH={BH_TOTAL} S=4096 D={D}, fp16, "
+                                f"{'causal' if causal else 'non-causal'})", "value": value,
                       "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                       "dtype": "f16 in, f32 softmax, f16 out", "data": "synthetic",
-                      "config": {"workload": "attention forward BH=256 S=4096 D=128, heads sharded over ranks",
+                      "config": {"workload": f"attention forward BH={BH_TOTAL} S=4096 D={D}, heads sharded over ranks",
                                  "values": "unit normal from a position hash, seeds 101, 101^888, 101^1776",
                                  "l2": "inputs exceed L2: Q,K,V,O = 1 GiB"},
                       "clocks": clocks.summary(), "gpu_launches": args.steps,
                       "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
                                    "unit": UNIT, "frac": value / world / peaks["bf16_tflops"], "traffic": None,
-                                   "kernel": "spork::attn_sm100::attn_fwd_kernel<128>",
+                                   "kernel": f"spork::attn_sm100::attn_fwd_kernel<{D}>",
                                    "frac_of_nominal_2250": value / world / 2250.0}}), flush=True)
+
+
+def run_shape(args, sp, torch, dev):
+    """One single-GPU GEMM of a given shape through the default entry point, warm-up plus timed launches with
+    one event pair each: the command profiler captures of the skinny-N configurations run."""
+    M, N, K = (int(x) for x in args.shape.split(","))
+    a = torch.empty((M, K), dtype=torch.float16, device=dev)
+    b = torch.empty((N, K), dtype=torch.float16, device=dev)
+    c = torch.empty((M, N), dtype=torch.float32, device=dev)
+    sp.init_test_data(a, sp.DATA_UNIFORM_PM1, sp.SEED_A)
+    sp.init_test_data(b, sp.DATA_UNIFORM_PM1, sp.SEED_B, transpose_rule=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2: written between launches
+    for _ in range(args.warmup):
+        sp.matmul_sm100(a, b, c)
+    sp.status()
+    times = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        sp.matmul_sm100(a, b, c)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    sp.status()
+    ms = statistics.median(times)
+    nbytes = 2 * M * K + 2 * N * K + 4 * M * N
+    print(json.dumps({"kernel_only": True, "shape": [M, N, K], "ms_per_step": ms, "value": 2.0 * M * N * K / ms / 1e9,
+                      "unit": UNIT, "hbm_gbs": nbytes / ms / 1e6, "l2": "flushed between launches"}), flush=True)
 
 
 def run_reference(args, rank, world):
@@ -263,6 +303,13 @@ def main():
                     help="gemm = the headline line; attention = the companion forward kernel, heads sharded over ranks")
     ap.add_argument("--kernel-only", action="store_true",
                     help="profiling runs: only the warm-up and timed launches (no end-to-end, library or CPU legs)")
+    ap.add_argument("--shape", default=None,
+                    help="M,N,K of another single-GPU GEMM for --kernel-only runs (the skinny-N configurations)")
+    ap.add_argument("--heads", type=int, default=256,
+                    help="--workload attention: number of (batch, head) slices (256 is the configuration's; fewer "
+                         "for a small profiler capture)")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
+    ap.add_argument("--causal", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -293,6 +340,10 @@ def main():
         run_attention(args, sp, torch, dist, dev, rank, world)
         if dist is not None:
             dist.destroy_process_group()
+        return
+
+    if args.shape is not None:
+        run_shape(args, sp, torch, dev)
         return
 
     # ---- operands: this rank's slab of A, a replica of B (made on rank 0, broadcast over NVLink)
@@ -373,22 +424,27 @@ def main():
     e2e_ok = bool(torch.equal(hc.to(dev), c))
 
     # ---- context: the vendor library on the same operands, same protocol (not the product path)
-    cublas_tflops = None
+    # fp16 in / fp32 out is the like-for-like figure (the call of gemm/gemm_test.cu:249-261 with fp16 operands);
+    # fp16 out writes half the result bytes and is shown beside it.
+    cublas_tflops = {"f16_in_f32_out": None, "f16_in_f16_out": None}
     if rank == 0:
-        try:
-            bt = b.t()
-            for _ in range(3):
-                torch.mm(a, bt)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(min(args.steps, 50)):
-                torch.mm(a, bt)
-            e1.record()
-            torch.cuda.synchronize()
-            cublas_tflops = FLOPS_PER_STEP / (e0.elapsed_time(e1) / min(args.steps, 50) * 1e-3) / 1e12
-        except Exception:
-            cublas_tflops = None
+        bt = b.t()
+        n_lib = min(args.steps, 50)
+        for key, call in (("f16_in_f32_out", lambda: torch.mm(a, bt, out_dtype=torch.float32)),
+                          ("f16_in_f16_out", lambda: torch.mm(a, bt))):
+            try:
+                for _ in range(3):
+                    call()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(n_lib):
+                    call()
+                e1.record()
+                torch.cuda.synchronize()
+                cublas_tflops[key] = FLOPS_PER_STEP / (e0.elapsed_time(e1) / n_lib * 1e-3) / 1e12
+            except Exception:
+                cublas_tflops[key] = None
 
     if rank != 0:
         if dist is not None:
@@ -398,16 +454,18 @@ def main():
     peaks = measured_peaks()
     other = other_configs(sp, torch, dev, peaks) if world == 1 else None
     avg_launch_ms = sum(launch_ms) / len(launch_ms)
+    sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     achieved = FLOPS_PER_STEP / (avg_launch_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES,
+                "traffic_source": NCU_TRAFFIC_SOURCE,
                 "peak_kind": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['bf16_tflops_sustained']})",
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "kernel": "spork::gemm_sm100::gemm_kernel<2,256>", "algorithmic_bytes": BYTES_PER_STEP,
                 "avg_launch_ms": avg_launch_ms, "min_launch_ms": min(launch_ms),
                 "sm_mhz_in_kernel": in_kernel_mhz,
                 "frac_of_peak_at_that_clock": (FLOPS_PER_STEP / (launch_ms[-1] * 1e-3) / 1e12) /
-                                              (148 * 8192 * in_kernel_mhz * 1e6 / 1e12) if in_kernel_mhz > 0 else None}
+                                              (sm_count * 8192 * in_kernel_mhz * 1e6 / 1e12) if in_kernel_mhz > 0 else None}
 
     # ---- the same launch repeated for a few hundred milliseconds: what the part sustains once the power cap
     # has pulled the clock down (reported beside the headline, not instead of it)
@@ -444,7 +502,8 @@ def main():
                     "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
             "gpu_launches": args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline, "sustained": sustained,
             "other_configs": other,
-            "context": {"cublas_fp16_tflops_same_protocol": cublas_tflops, "frac_of_nominal_fp16_peak": value / (2250.0 * world)}}
+            "context": {"cublas_tflops_same_protocol": cublas_tflops,
+                        "frac_of_nominal_fp16_peak": value / (2250.0 * world)}}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

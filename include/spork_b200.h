@@ -135,9 +135,21 @@ int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
  * 2 for skinny HBM-bound problems).  Bits 4..6 of
  * l2_hints switch diagnostic experiments whose RESULTS ARE UNDEFINED (0x10 the
  * epilogue drops its stores, 0x20 the producer stops loading after the first
- * ring fill, 0x40 stores go straight from registers).  The reference
+ * ring fill, 0x40 stores go straight from registers).  Bits 10..11: 256 x 512
+ * tiles per CTA pair for problems whose tile is left to the library (0 = chosen
+ * per shape, 1 = never, 2 = always); bits 12..15: K blocks by which one half of
+ * such a tile runs ahead of the other at the tile's ends (0 = default);
+ * bits 16..23: their raster group (0 = default).  spork_gemm_sm100_tuning reads
+ * the knobs back.  The reference
  * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
 int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);
+
+/* The knobs as later launches will see them: out[0] = ring depth, [1] = raster
+ * group, [2] = the L2 hint bits a launch carries (bit 0 = A evict-last, bit 1 = B
+ * evict-last, bit 2 = B evict-first; 0 = none), [3] = poll back-off, [4] =
+ * experiment bits, [5] = column blocks per stage, [6] = 256 x 512 tile choice,
+ * [7] = its skew, [8] = its raster group.  No counterpart in the reference. */
+int spork_gemm_sm100_tuning(int* out, int capacity);
 
 /* Host-only view of how a launch would be laid out (no CUDA call; usable without a
  * GPU).  Arguments as for the _ex entry point, plus the SM count to plan for and

@@ -30,5 +30,6 @@ from .api import (  # noqa: F401
     matmul_sm100_tf32,
     status,
     tune,
+    tuning,
     version,
 )

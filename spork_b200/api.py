@@ -75,6 +75,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_last_clock_mhz.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
         L.spork_gemm_sm100_tune.restype = i32
+        L.spork_gemm_sm100_tuning.argtypes = [ctypes.POINTER(i32), i32]
+        L.spork_gemm_sm100_tuning.restype = i32
         L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]
         L.spork_gemm_sm100_status.restype = i32
         L.spork_gemm_sm100_htod_f16f32.argtypes = [u32, u32, u32, vp, vp, vp]
@@ -132,6 +134,14 @@ def _dev_ptr(t, dtype, what: str) -> int:
     return int(t.data_ptr())
 
 
+def _same_device(first, *others) -> None:
+    """All operands of a launch must live on one GPU: the kernel runs on the first one's device and would
+    otherwise read or write addresses that mean nothing there."""
+    for t in others:
+        if t.device != first.device:
+            raise ValueError(f"tensors are on different devices: {first.device} and {t.device}")
+
+
 def matmul_sm100_supports(M: int, N: int, K: int) -> bool:
     return bool(lib().spork_gemm_sm100_supports(M, N, K))
 
@@ -154,6 +164,7 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
         c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     if tuple(c.shape) != (M, N):
         raise ValueError(f"c must be {(M, N)}, got {tuple(c.shape)}")
+    _same_device(a, b, c)
     pa = _dev_ptr(a, torch.float16, "a")
     pb = _dev_ptr(b, torch.float16, "b")
     pc = _dev_ptr(c, torch.float32, "c")
@@ -183,6 +194,7 @@ def matmul_sm100_batched(a, b, c=None, *, variant: int = 0, split_k: int = 1, st
         c = torch.empty((L, M, N), dtype=torch.float32, device=a.device)
     if tuple(c.shape) != (L, M, N):
         raise ValueError(f"c must be {(L, M, N)}, got {tuple(c.shape)}")
+    _same_device(a, b, c)
     pa = _dev_ptr(a, torch.float16, "a")
     pb = _dev_ptr(b, torch.float16, "b")
     pc = _dev_ptr(c, torch.float32, "c")
@@ -202,6 +214,9 @@ def matmul_sm100_tf32(a, b, c=None, *, variant: int = 0, split_k: int = 1, strea
         raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
     if c is None:
         c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    if tuple(c.shape) != (M, N):
+        raise ValueError(f"c must be {(M, N)}, got {tuple(c.shape)}")
+    _same_device(a, b, c)
     pa, pb, pc = (_dev_ptr(t, torch.float32, n) for t, n in ((a, "a"), (b, "b"), (c, "c")))
     with torch.cuda.device(a.device):
         rc = lib().spork_gemm_sm100_tf32f32(M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
@@ -216,9 +231,22 @@ def last_clock_mhz(stream=None) -> float:
     return float(mhz.value)
 
 
-def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0) -> None:
-    """Process-wide tuning knobs of later GEMM launches (see spork_gemm_sm100_tune in the header)."""
-    _check(lib().spork_gemm_sm100_tune(stages, group_m, l2_hints, backoff_ns), "spork_gemm_sm100_tune")
+def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0, *, experiment: int = 0,
+         k_atoms: int = 0, wide: int = 0, wide_skew: int = 0, wide_group_m: int = 0) -> None:
+    """Process-wide tuning knobs of later GEMM launches (see spork_gemm_sm100_tune in the header).
+
+    ``l2_hints`` may carry the packed upper bits itself (the C form); the keyword arguments are OR-ed in."""
+    packed = l2_hints | ((experiment & 7) << 4) | ((k_atoms & 3) << 8) | ((wide & 3) << 10) | \
+        ((wide_skew & 15) << 12) | ((wide_group_m & 255) << 16)
+    _check(lib().spork_gemm_sm100_tune(stages, group_m, packed, backoff_ns), "spork_gemm_sm100_tune")
+
+
+def tuning() -> dict:
+    """The knobs as the next launch will see them (``l2_hints`` is the effective hint mask)."""
+    out = (ctypes.c_int * 9)()
+    _check(lib().spork_gemm_sm100_tuning(out, 9), "spork_gemm_sm100_tuning")
+    keys = ("stages", "group_m", "l2_hints", "backoff_ns", "experiment", "k_atoms", "wide", "wide_skew", "wide_group_m")
+    return dict(zip(keys, (int(v) for v in out)))
 
 
 def status(stream=None, device=None) -> None:
@@ -299,9 +327,17 @@ def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None, causal: b
     (the reference interface's type)."""
     import torch
 
+    if q.dim() != 3:
+        raise ValueError(f"q must be (BH, S, D), got {tuple(q.shape)}")
     BH, S, D = q.shape
     if o is None:
         o = torch.empty_like(q)
+    # every tensor map and every store is sized from q: a shorter k or v, or a smaller o, would be read or
+    # written past its end
+    for t, name in ((k, "k"), (v, "v"), (o, "o")):
+        if tuple(t.shape) != (BH, S, D):
+            raise ValueError(f"{name} must have q's shape {(BH, S, D)}, got {tuple(t.shape)}")
+    _same_device(q, k, v, o)
     if scale is None:
         scale = 1.0 / (D ** 0.5)
     dt = q.dtype

@@ -101,6 +101,8 @@ struct Params {
     // K blocks per CTA group and reduce-added into a zeroed C; the first `dp_tiles` run whole.
     uint32_t dp_tiles, sk_tiles;
     uint32_t sk_share, sk_extra; // group g owns sk_share (+1 if g < sk_extra) K blocks of the stream-K part
+    uint32_t wide_skew;          // 256 x 512 tiles: K blocks of one accumulator half issued ahead of the other at both
+                                 // ends of a tile (1 .. ring depth)
     uint32_t experiment;         // diagnostics only, results undefined: bit 0 = epilogue drops its stores,
                                  // bit 1 = producer stops issuing loads once the ring has been filled once,
                                  // bit 2 = epilogue stores straight from registers (no shared-memory staging)
@@ -563,6 +565,14 @@ __global__ void __launch_bounds__(256) zero_tiles_kernel(const Params p, uint32_
     }
 }
 
+}  // namespace gemm_sm100
+}  // namespace spork
+
+#include "gemm_sm100_wide.cuh"
+
+namespace spork {
+namespace gemm_sm100 {
+
 // ------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -716,6 +726,9 @@ struct Tuning {
     int backoff_ns = 0;
     int experiment = 0;
     int k_atoms = 0;      // 0 = choose; 1 / 2 = 128-byte column blocks per stage
+    int wide = 0;         // 256 x 512 tiles: 0 = choose, 1 = never, 2 = whenever the shape allows
+    int wide_skew = 0;    // 0 = default (ring depth)
+    int wide_group_m = 0; // 0 = default raster group of the 256 x 512 kernel
 };
 static Tuning g_tuning;
 
@@ -819,9 +832,103 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     return (int)e;
 }
 
+// The 256 x 512 kernel: same plan, maps and status word as launch<2, ...>.
+template <bool kTf32>
+static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
+                       int max_ctas, DeviceState& dev, cudaStream_t stream)
+{
+    using Cfg = WideConfig;
+    auto kernel = gemm_wide_kernel<kTf32>;
+    constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
+    constexpr CUtensorMapDataType kOperandType = kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    constexpr uint32_t kOperandBytes = kTf32 ? 4 : 2;
+
+    static std::once_flag attr_once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    std::call_once(attr_once[dev.ordinal], [&] {
+        attr_err[dev.ordinal] =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    });
+    if (attr_err[dev.ordinal] != cudaSuccess) {
+        return (int)attr_err[dev.ordinal];
+    }
+
+    Params p{};
+    uint32_t groups = 1;
+    plan_launch(p, groups, M, N, K, 2 * kBlockM, kWideN, 2, kElemsK, split_k, false, max_ctas, dev.sm_count, 1);
+    p.C = C;
+    p.status = dev.status_word;
+    const Tuning tune = g_tuning;
+    p.stages = (uint32_t)kWideStages;
+    p.group_m = tune.wide_group_m >= 1 ? (uint32_t)tune.wide_group_m : (uint32_t)kWideGroupM;
+    p.l2_hints = effective_l2_hints(tune.l2_hints);
+    p.backoff_ns = (uint32_t)tune.backoff_ns;
+    p.experiment = (uint32_t)tune.experiment & 1u;
+    p.wide_skew = tune.wide_skew >= 1 ? (uint32_t)tune.wide_skew : (uint32_t)kWideStages;
+
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    int rc = make_tmap_2d(&tmap_a, kOperandType, kOperandBytes, A, M, K, kBlockM, kElemsK);
+    if (rc) {
+        return rc;
+    }
+    rc = make_tmap_2d(&tmap_b, kOperandType, kOperandBytes, B, N, K, kWideHalfN / 2, kElemsK);
+    if (rc) {
+        return rc;
+    }
+    if (p.use_tma_store) {
+        rc = make_tmap_2d(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, M, N, 32, kEpiCols);
+        if (rc) {
+            return rc;
+        }
+    } else {
+        tmap_c = tmap_a;  // never dereferenced
+    }
+    if (p.split_k > 1) {
+        const cudaError_t e = cudaMemsetAsync(C, 0, sizeof(float) * (size_t)M * N, stream);
+        if (e != cudaSuccess) {
+            return (int)e;
+        }
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(groups * 2, 1, 1);
+    cfg.blockDim = dim3(kWideThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, tmap_c, p);
+}
+
 static bool aligned16(const void* p)
 {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// Whether a problem whose tile is left to the library runs with 256 x 512 tiles.  They move a quarter fewer
+// operand bytes per FLOP, which is what a compute-bound problem at the power limit is short of, but their
+// tiles are twice as coarse: the problem must fill at least two waves of them, waste little of the last
+// tile column, and be deep enough for the skewed tile ends to be a small part of a tile.
+static bool want_wide_tiles(uint32_t M, uint32_t N, uint32_t K, int max_ctas, int sm_count)
+{
+    if (g_tuning.wide == 1) {
+        return false;
+    }
+    if (g_tuning.wide == 2) {
+        return true;
+    }
+    uint32_t groups = (uint32_t)sm_count / 2u;
+    if (max_ctas > 0 && (uint32_t)max_ctas / 2u < groups) {
+        groups = (uint32_t)max_ctas / 2u;
+    }
+    const uint64_t tiles_n = (N + kWideN - 1) / kWideN;
+    const uint64_t tiles = (uint64_t)((M + 255) / 256) * tiles_n;
+    const uint64_t padded_n = tiles_n * kWideN;
+    return groups > 0 && tiles >= 2ull * groups && K >= 1024 && (padded_n - N) * 16 <= N;
 }
 
 static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int block_n,
@@ -854,6 +961,16 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     if (rc) {
         return rc;
     }
+    const bool tile_left_to_library = cta_group == 0;
+    if (block_n == kWideN) {
+        // 256 x 512 tiles on request: CTA pairs only, one matrix, output-stationary or split-K
+        if ((cta_group != 0 && cta_group != 2) || batches != 1 || split_k < 0) {
+            return SPORK_ERR_BAD_ARGUMENT;
+        }
+        const uint32_t sk = split_k == 0 ? 1u : (uint32_t)split_k;
+        return tf32 ? launch_wide<true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream)
+                    : launch_wide<false>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+    }
     if (cta_group == 0) {
         // The caller left the tile to the library.  A problem that fills a small part of one wave and
         // has a short K is bound by latencies, not by throughput: a single CTA per tile starts 1.5-2 us
@@ -873,18 +990,31 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     }
     const bool stream_k = split_k == -1;
     const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
+    if (tile_left_to_library && cta_group == 2 && block_n == 256 && batches == 1 && sk == 1 && !stream_k &&
+        want_wide_tiles(M, N, K, max_ctas, dev->sm_count)) {
+        return tf32 ? launch_wide<true>(M, N, K, A, B, C, 1, max_ctas, *dev, stream)
+                    : launch_wide<false>(M, N, K, A, B, C, 1, max_ctas, *dev, stream);
+    }
     // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
     // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.
     const uint64_t out_tiles =
         (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
-    const bool wide_k = !tf32 && cta_group == 2 &&
-                        (g_tuning.k_atoms == 2 || (g_tuning.k_atoms == 0 && block_n <= 128 &&
-                                                   out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
-    if (wide_k) {
+    const bool wide_k = !tf32 && (g_tuning.k_atoms == 2 ||
+                                  (cta_group == 2 && g_tuning.k_atoms == 0 && block_n <= 128 &&
+                                   out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
+    if (wide_k && cta_group == 2) {
         switch (block_n) {
         case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
         case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
         case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        default: return SPORK_ERR_BAD_ARGUMENT;
+        }
+    }
+    if (wide_k && cta_group == 1) {
+        switch (block_n) {
+        case 64: return launch<1, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 128: return launch<1, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 256: return launch<1, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
@@ -1156,8 +1286,8 @@ extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K
 static bool plan_from_args(spork::gemm_sm100::Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K,
                            int block_n, int cta_group, int split_k, int max_ctas, int sm_count, int tf32)
 {
-    if ((block_n != 64 && block_n != 128 && block_n != 256) || (cta_group != 1 && cta_group != 2) ||
-        split_k < -1 || max_ctas < 0 || sm_count < cta_group) {
+    if ((block_n != 64 && block_n != 128 && block_n != 256 && block_n != 512) || (cta_group != 1 && cta_group != 2) ||
+        (block_n == 512 && (cta_group != 2 || split_k == -1)) || split_k < -1 || max_ctas < 0 || sm_count < cta_group) {
         return false;
     }
     if (split_k == 0) {
@@ -1234,16 +1364,34 @@ extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x2FF || backoff_ns < 0 || backoff_ns > 100000) {
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0xFFFFFF || ((l2_hints >> 8) & 3) > 2 ||
+        ((l2_hints >> 10) & 3) > 2 || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     spork::gemm_sm100::g_tuning.experiment = (l2_hints >> 4) & 7;  // bits 4..6: diagnostic experiments (see Params)
-    spork::gemm_sm100::g_tuning.k_atoms = l2_hints >> 8;           // bits 8..9: column blocks per stage, 0 = choose
-    l2_hints &= 7;
+    spork::gemm_sm100::g_tuning.k_atoms = (l2_hints >> 8) & 3;     // bits 8..9: column blocks per stage, 0 = choose
+    spork::gemm_sm100::g_tuning.wide = (l2_hints >> 10) & 3;       // bits 10..11: 256 x 512 tiles: choose / never / always
+    spork::gemm_sm100::g_tuning.wide_skew = (l2_hints >> 12) & 15; // bits 12..15: their skew, 0 = default
+    spork::gemm_sm100::g_tuning.wide_group_m = (l2_hints >> 16) & 255;  // bits 16..23: their raster group, 0 = default
+    l2_hints &= 15;   // bit 3 = "no hints at all" must survive (see effective_l2_hints)
     spork::gemm_sm100::g_tuning.stages = stages;
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
     spork::gemm_sm100::g_tuning.l2_hints = l2_hints;
     spork::gemm_sm100::g_tuning.backoff_ns = backoff_ns;
+    return 0;
+}
+
+extern "C" int spork_gemm_sm100_tuning(int* out, int capacity)
+{
+    if (!out || capacity < 9) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    const spork::gemm_sm100::Tuning t = spork::gemm_sm100::g_tuning;
+    const int vals[9] = {t.stages, t.group_m, (int)spork::gemm_sm100::effective_l2_hints(t.l2_hints), t.backoff_ns,
+                         t.experiment, t.k_atoms, t.wide, t.wide_skew, t.wide_group_m};
+    for (int i = 0; i < 9; ++i) {
+        out[i] = vals[i];
+    }
     return 0;
 }
 
@@ -1271,11 +1419,11 @@ extern "C" int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, cons
     if (variant == 0) {
         block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
     }
-    if (block_n != 64 && block_n != 128 && block_n != 256) {
+    if (block_n != 64 && block_n != 128 && block_n != 256 && block_n != 512) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
-    return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, 2, split_k, 0, static_cast<cudaStream_t>(stream),
-                                       true);
+    return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, variant == 0 ? 0 : 2, split_k, 0,
+                                       static_cast<cudaStream_t>(stream), true);
 }
 
 extern "C" int spork_gemm_sm100_f16f32_batched(uint32_t L, uint32_t M, uint32_t N, uint32_t K, const void* A,
@@ -1299,7 +1447,7 @@ extern "C" int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const
     if (variant == 0) {
         block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
     }
-    if (block_n != 64 && block_n != 128 && block_n != 256) {
+    if (block_n != 64 && block_n != 128 && block_n != 256 && block_n != 512) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, variant == 0 ? 0 : SPORK_DEFAULT_CTA_GROUP, 1, 0,

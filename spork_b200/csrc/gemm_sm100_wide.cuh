@@ -1,0 +1,354 @@
+// 256 x 512 output tiles per CTA pair: the large-problem variant of the sm_100a GEMM.
+//
+// Why: with uniform random operands the 256 x 256 kernel runs into the board's power limit, and a
+// third of that power moves operand bytes from L2 into shared memory (every CTA pulls 32 KB per
+// 64-deep K step).  A 256 x 512 tile needs A once for two 256-column halves of B: 48 KB per CTA for
+// twice the FLOPs, a quarter fewer bytes per FLOP, and a wave of tiles touches fewer distinct strips
+// of A and B, so DRAM reads fall as well.
+//
+// The two halves H0, H1 of a tile are two 256-column accumulators that fill all 512 columns of
+// tensor memory, so there is no second buffer to hide the epilogue behind.  Instead the MMA order
+// is skewed at both ends of a tile: the last G K-blocks are issued for H0 first (its accumulator is
+// then final and the epilogue takes it) and only then for H1; the next tile begins with G K-blocks
+// of H0 alone, into the columns just freed, while H1 is being taken.  In between, H0 and H1
+// alternate per K-block so that a ring stage is released as soon as possible.  G is bounded by the
+// ring depth (4 stages of 48 KB).
+//
+// The epilogue warps (8) copy a half accumulator from tensor memory into registers in one go
+// (128 fp32 per thread), release the columns at once, and only then write the registers out
+// through a swizzled shared-memory slab and TMA stores: the tensor pipe waits for the copy into
+// registers, not for the stores.
+//
+// Same operand layout, tensor maps, work-item list, raster and bounded waits as gemm_kernel.
+#pragma once
+
+namespace spork {
+namespace gemm_sm100 {
+
+constexpr int kWideHalfN = 256;               // columns of one accumulator half = N of one MMA
+constexpr int kWideN = 2 * kWideHalfN;        // columns of a tile
+constexpr int kWideEpiWarps = 8;
+constexpr int kWideThreads = 32 * (2 + kWideEpiWarps);
+constexpr int kWideStages = 4;
+constexpr int kWideGroupM = 8;
+
+struct WideConfig {
+    static constexpr int kABytes = kBlockM * kBlockK * 2;               // this CTA's 128 rows of A
+    static constexpr int kBHalfBytes = (kWideHalfN / 2) * kBlockK * 2;  // this CTA's 128 rows of one half of B
+    static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;       // 48 KB
+    static constexpr int kStagingBytes = kWideEpiWarps * kSlabBytes;    // one slab per epilogue warp
+    static constexpr int kBarrierBytes = 1024;
+    static constexpr int kSmemBytes = 1024 + kWideStages * kStageBytes + kStagingBytes + kBarrierBytes;
+    static constexpr int kTmemCols = 512;
+    static_assert(kSmemBytes <= kMaxSmem, "shared memory limit");
+};
+
+struct WideBarriers {
+    uint64_t full[kWideStages];
+    uint64_t empty[kWideStages];
+    uint64_t tmem_full[2];    // one per accumulator half
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+// Sizes of the chunks a tile's K-blocks are issued in.  Inside a chunk the MMAs of H0 come first, then
+// those of H1.  The first and the last chunk are `skew` K-blocks long (shorter tiles are cut in two, or
+// run as one chunk), the ones between are single K-blocks.  Pure arithmetic, shared with the host-side
+// model of the schedule.
+__host__ __device__ __forceinline__ uint32_t wide_chunk(uint32_t n, uint32_t done, uint32_t skew)
+{
+    const uint32_t rem = n - done;
+    if (done == 0) {
+        return n >= 2 * skew ? skew : (n > skew ? n - n / 2 : n);
+    }
+    return rem <= skew ? rem : 1u;
+}
+
+template <bool kTf32>
+__global__ void __launch_bounds__(kWideThreads, 1)
+gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p)
+{
+    using Cfg = WideConfig;
+    constexpr int CG = 2;
+    extern __shared__ uint8_t smem_raw[];
+
+    const uint32_t warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);
+    const uint32_t lane = threadIdx.x % 32;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool is_leader = cta_rank == 0;
+    const uint32_t group_id = blockIdx.x / CG;
+    const uint32_t num_groups = gridDim.x / CG;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t ring_base = smem_base;
+    const uint32_t staging_base = ring_base + kWideStages * Cfg::kStageBytes;
+    WideBarriers* bars =
+        reinterpret_cast<WideBarriers*>(smem_raw + (staging_base + Cfg::kStagingBytes - smem_u32(smem_raw)));
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWideStages; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(smem_u32(&bars->tmem_full[h]), 1);
+            mbar_init(smem_u32(&bars->tmem_empty[h]), kWideEpiWarps * CG);
+        }
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+        prefetch_tensormap(&tmap_c);
+    }
+    if (warp == 1) {
+        tmem_alloc<CG>(smem_u32(&bars->tmem_base), Cfg::kTmemCols);
+        tmem_relinquish<CG>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_arrive_release();   // the peer's barriers must exist before anything arrives on them
+    cluster_wait_acquire();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    const uint32_t num_items = group_item_count(p, group_id, num_groups);
+    constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            const uint64_t pol_a = (p.l2_hints & 1u) ? l2_policy_evict_last() : l2_policy_evict_normal();
+            const uint64_t pol_b = (p.l2_hints & 2u) ? l2_policy_evict_last()
+                                   : (p.l2_hints & 4u) ? l2_policy_evict_first() : l2_policy_evict_normal();
+            for (uint32_t item = 0; item < num_items && ok; ++item) {
+                const WorkItem w = group_item(p, group_id, num_groups, item);
+                const int32_t a_row = (int32_t)(w.m_tile * (kBlockM * CG) + cta_rank * kBlockM);
+                const int32_t b_row = (int32_t)(w.n_tile * kWideN + cta_rank * (kWideHalfN / 2));
+                for (uint32_t kb = w.kb_begin; kb < w.kb_end; ++kb) {
+                    if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag, p.backoff_ns)) {
+                        report_timeout(p, abort_flag, 1, stage);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
+                    const uint32_t sb = sa + Cfg::kABytes;
+                    const uint32_t full = smem_u32(&bars->full[stage]);
+                    if (is_leader) {
+                        mbar_arrive_expect_tx(full, Cfg::kStageBytes * 2);  // both CTAs' bytes land on the leader's barrier
+                    }
+                    const uint32_t leader_full = map_to_cta(full, 0);
+                    const int32_t x = (int32_t)(kb * kElemsK);
+                    tma_load_2d_pair_hint(sa, &tmap_a, leader_full, x, a_row, pol_a);
+                    tma_load_2d_pair_hint(sb, &tmap_b, leader_full, x, b_row, pol_b);
+                    tma_load_2d_pair_hint(sb + Cfg::kBHalfBytes, &tmap_b, leader_full, x, b_row + kWideHalfN, pol_b);
+                    if (++stage == kWideStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (is_leader) {
+            const bool elected = elect_one();
+            constexpr uint32_t idesc = kTf32 ? umma_idesc_tf32_f32(kBlockM * CG, kWideHalfN)
+                                             : umma_idesc_f16_f32(kBlockM * CG, kWideHalfN);
+            const uint32_t skew = p.wide_skew < 1u ? 1u : (p.wide_skew > (uint32_t)kWideStages ? (uint32_t)kWideStages
+                                                                                                : p.wide_skew);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t item = 0; item < num_items && ok; ++item) {
+                const WorkItem w = group_item(p, group_id, num_groups, item);
+                const uint32_t n = w.kb_end - w.kb_begin;
+                const uint32_t tile_phase = item & 1u;
+                uint32_t done = 0;
+                while (done < n && ok) {
+                    const uint32_t g = wide_chunk(n, done, skew);
+                    const bool first = done == 0;
+                    const bool last = done + g == n;
+#pragma unroll 1
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        if (first) {
+                            // the epilogue must have taken this half of the previous tile
+                            if (!__all_sync(0xFFFFFFFFu, mbar_wait<true>(smem_u32(&bars->tmem_empty[h]),
+                                                                         tile_phase ^ 1u, abort_flag))) {
+                                if (elected) {
+                                    report_timeout(p, abort_flag, 2, 0x40 + h);
+                                }
+                                ok = false;
+                                break;
+                            }
+                            tcgen05_fence_after();
+                        }
+                        const uint32_t tmem_d = tmem_base + h * kWideHalfN;
+                        uint32_t s = stage, ph = phase;
+                        for (uint32_t j = 0; j < g; ++j) {
+                            if (h == 0) {
+                                if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag))) {
+                                    if (elected) {
+                                        report_timeout(p, abort_flag, 2, s);
+                                    }
+                                    ok = false;
+                                    break;
+                                }
+                                tcgen05_fence_after();
+                            }
+                            const uint32_t sa = ring_base + s * Cfg::kStageBytes;
+                            if (elected) {
+                                const uint64_t desc_a = umma_desc_kmajor_sw128(sa);
+                                const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes + h * Cfg::kBHalfBytes);
+#pragma unroll
+                                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                                    const uint32_t acc = (!first || j != 0 || k != 0) ? 1u : 0u;
+                                    if (kTf32) {
+                                        umma_tf32_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                                    } else {
+                                        umma_f16_ss<CG>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, acc);
+                                    }
+                                }
+                                if (h == 1) {
+                                    // both halves have read the stage: free it in both CTAs
+                                    const uint32_t empty = smem_u32(&bars->empty[s]);
+                                    umma_commit<CG>(empty);
+                                    umma_commit<CG>(map_to_cta(empty, 1));
+                                }
+                            }
+                            if (++s == kWideStages) {
+                                s = 0;
+                                ph ^= 1u;
+                            }
+                        }
+                        if (!ok) {
+                            break;
+                        }
+                        if (last && elected) {
+                            // this half is final: wake the epilogue warps of both CTAs
+                            const uint32_t tfull = smem_u32(&bars->tmem_full[h]);
+                            umma_commit<CG>(tfull);
+                            umma_commit<CG>(map_to_cta(tfull, 1));
+                        }
+                        if (h == 1) {
+                            stage = s;
+                            phase = ph;
+                        }
+                    }
+                    done += g;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp % 4;                       // TMEM lanes [32*quarter, +32) belong to this warp
+        const uint32_t part = (warp - kEpilogueWarp0) / 4;       // which 128 of a half's 256 columns
+        const uint32_t slab = staging_base + (warp - kEpilogueWarp0) * kSlabBytes;
+        bool ok = true;
+        for (uint32_t item = 0; item < num_items && ok; ++item) {
+            const WorkItem w = group_item(p, group_id, num_groups, item);
+            const uint32_t tile_phase = item & 1u;
+            const uint32_t row0 = w.m_tile * (kBlockM * CG) + cta_rank * kBlockM + quarter * 32;
+            const bool rows_live = row0 < p.M && w.kb_begin < w.kb_end;
+#pragma unroll 1
+            for (uint32_t h = 0; h < 2; ++h) {
+                if (!mbar_wait(smem_u32(&bars->tmem_full[h]), tile_phase, abort_flag, p.backoff_ns)) {
+                    if (lane == 0) {
+                        report_timeout(p, abort_flag, 3, 0x40 + h);
+                    }
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + h * kWideHalfN + part * 128u;
+                uint32_t r[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld_32x32b_x32(taddr + c * kEpiCols, r[c]);
+                }
+                tmem_ld_wait();
+                // the columns are free again as soon as they sit in registers
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[h]), 0));
+                }
+                const uint32_t col0 = w.n_tile * kWideN + h * kWideHalfN + part * 128u;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t col = col0 + c * kEpiCols;
+                    if (!rows_live || col >= p.N || (p.experiment & 1u)) {
+                        continue;  // warp-uniform
+                    }
+                    if (p.use_tma_store) {
+                        if (lane == 0) {
+                            bulk_wait_group_read<0>();  // the previous store has read the slab
+                        }
+                        __syncwarp();
+                        const uint32_t row_addr = slab + lane * 128u;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
+                                         r[c][4 * j + 2], r[c][4 * j + 3]);
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (w.reduce) {
+                                tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
+                            } else {
+                                tma_store_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
+                            }
+                            bulk_commit_group();
+                        }
+                    } else {
+                        const uint32_t row = row0 + lane;
+                        if (row < p.M) {
+                            float* dst = p.C + (size_t)row * p.N + col;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (col + j < p.N) {
+                                    if (w.reduce) {
+                                        atomicAdd(dst + j, __uint_as_float(r[c][j]));
+                                    } else {
+                                        dst[j] = __uint_as_float(r[c][j]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+            bulk_wait_group<0>();
+        }
+    }
+
+    // ------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<CG>(tmem_base, Cfg::kTmemCols);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[2] = (unsigned long long)clock64();
+        probe[3] = global_timer_ns();
+    }
+}
+
+}  // namespace gemm_sm100
+}  // namespace spork

@@ -5,7 +5,7 @@ imported whole because it loads a shared library at top level), executed on
 torch CPU, and their inputs/outputs stored.  Nothing of the reference is copied
 into this repository; only the numbers are.
 
-    python tests/golden/make_attn_golden.py [/path/to/reference]
+    python tests/golden/make_attn_golden.py /path/to/reference
 
 Inputs are rounded to fp16 first (the kernels under test take fp16), the
 reference math then runs in fp32 on those values.
@@ -18,7 +18,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_attn_golden.py /path/to/reference")
+REF = sys.argv[1]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -58,3 +58,42 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(api, "_LIB_PATH", os.path.join(ROOT, "no_such_dir", "libspork_b200.so"))
     with pytest.raises(FileNotFoundError):
         api.lib()
+
+
+def test_python_wrappers_reject_mismatched_shapes_before_any_launch(sp):
+    """Tensor maps and stores are sized from the first operand: the wrappers refuse operands of another
+    shape instead of letting a kernel run past an allocation.  CPU tensors do: the shape check comes first."""
+    import torch
+
+    q = torch.zeros((2, 256, 64), dtype=torch.float16)
+    with pytest.raises(ValueError):
+        sp.attn_fwd(q, q[:, :128].contiguous(), q)          # shorter k (a cross-attention call)
+    with pytest.raises(ValueError):
+        sp.attn_fwd(q, q, q[:, :, :32].contiguous())        # narrower v
+    with pytest.raises(ValueError):
+        sp.attn_fwd(q, q, q, o=torch.zeros((1, 256, 64), dtype=torch.float16))  # o too small
+    with pytest.raises(ValueError):
+        sp.attn_fwd(q[0], q[0], q[0])
+    a = torch.zeros((128, 64))
+    b = torch.zeros((96, 64))
+    with pytest.raises(ValueError):
+        sp.matmul_sm100_tf32(a, b, torch.zeros((128, 64)))   # c must be (128, 96)
+    with pytest.raises(ValueError):
+        sp.matmul_sm100(a.half(), b.half(), torch.zeros((64, 96)))
+
+
+def test_tuning_knobs_round_trip_without_a_gpu(sp):
+    try:
+        sp.tune(l2_hints=8)                       # "no hints at all" must reach the launch as an empty mask
+        assert sp.tuning()["l2_hints"] == 0
+        sp.tune(l2_hints=4)
+        assert sp.tuning()["l2_hints"] == 4
+        sp.tune(stages=5, group_m=4, k_atoms=2, wide=2, wide_skew=2, wide_group_m=16, experiment=1)
+        t = sp.tuning()
+        assert (t["stages"], t["group_m"], t["k_atoms"], t["wide"], t["wide_skew"], t["wide_group_m"],
+                t["experiment"]) == (5, 4, 2, 2, 2, 16, 1)
+        assert sp.lib().spork_gemm_sm100_tune(0, 0, 3 << 10, 0) == 10001   # tile choice 3 does not exist
+    finally:
+        sp.tune()
+    assert sp.tuning() == {"stages": 0, "group_m": 8, "l2_hints": 3, "backoff_ns": 0, "experiment": 0, "k_atoms": 0,
+                           "wide": 0, "wide_skew": 0, "wide_group_m": 0}
