@@ -35,11 +35,12 @@ enum class gemm_sm100_k_mode
     automatic, // output_stationary, or split_k_outer with a split count chosen to fill the waves (few tiles, long K)
 };
 
-// The kernel takes the harness's hot layout only: A row-major, B stored N x K,
-// C row-major (gemm/gemm_test.cu:365); K must be a multiple of 8.
+// The kernel takes the harness's hot operand layout: A row-major, B stored N x K (gemm/gemm_test.cu:365);
+// K must be a multiple of 8.  C may be row-major or column-major: like matmul_sm90
+// (gemm/gemm_sm90.cu:1349-1355) the other one is produced by exchanging the operands, C^T = B A^T.
 inline bool matmul_sm100_supports(GPU_TensorsF16 t)
 {
-    return !t.a_col_major && t.b_col_major && !t.c_col_major && spork_gemm_sm100_supports(t.M, t.N, t.K) != 0;
+    return !t.a_col_major && t.b_col_major && spork_gemm_sm100_supports(t.M, t.N, t.K) != 0;
 }
 
 // Asynchronous on `stream`, like matmul_sm90.  Errors are printed, as the
@@ -50,6 +51,11 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
     if (!matmul_sm100_supports(t)) {
         fprintf(stderr, "matmul_sm100: unsupported layout or K %% 8 != 0 (M=%u N=%u K=%u)\n", t.M, t.N, t.K);
         return SPORK_ERR_UNSUPPORTED_SHAPE;
+    }
+    if (t.c_col_major) {
+        // a column-major M x N result is the row-major N x M result of the exchanged product
+        const GPU_TensorsF16 swapped{t.N, t.M, t.K, t.b, t.a, t.c, false, true, false};
+        t = swapped;
     }
     int rc;
     if ((k_mode == gemm_sm100_k_mode::split_k_outer && split_k > 1) || k_mode == gemm_sm100_k_mode::stream_k ||

@@ -139,16 +139,50 @@ int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
  * tiles per CTA pair for problems whose tile is left to the library (0 = chosen
  * per shape, 1 = never, 2 = always); bits 12..15: K blocks by which one half of
  * such a tile runs ahead of the other at the tile's ends (0 = default);
- * bits 16..23: their raster group (0 = default).  spork_gemm_sm100_tuning reads
+ * bits 16..23: their raster group (0 = default); bit 24: launches are plain
+ * stream-ordered kernels instead of programmatic dependents (by default a launch
+ * sets up its barriers and tensor memory while the previous kernel in the stream
+ * is still finishing on other SMs, and waits for it before touching global
+ * memory).  spork_gemm_sm100_tuning reads
  * the knobs back.  The reference
  * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
 int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);
+
+/* Host-side model of the kernels' barrier protocol (no GPU, no CUDA call): runs
+ * the roles of CTA group `group` of the launch plan of (M, N, K, block_n,
+ * cta_group, split_k >= 1 or -1, max_ctas, sm_count) - producers, TMA engines,
+ * MMA issuer, tensor pipe, epilogue warps - as cooperative agents over modelled
+ * mbarriers, in an interleaving drawn from `seed`, with a ring of `stages` stages
+ * and (block_n = 512) the given skew.  Returns 0 if every invariant held, else
+ * 1 = deadlock, 2 = a stage was refilled before it was read, 3 = an MMA read a
+ * stage that did not hold its K block, 4 = an MMA wrote an accumulator the
+ * epilogue still read, 5 = the epilogue read an accumulator that was not final,
+ * 6 = an output part was not written exactly once.  `inject` plants a protocol bug to show the checks notice:
+ * 1 = (block_n 512) a stage is released after the first half read it, 2 = the
+ * issuer does not wait for the accumulator, 3 = the producer does not wait for
+ * the stage; 0 = none.  stats (optional, 4 values): work items, MMA operations
+ * executed, scheduling steps, CTA groups of the plan.  Stands in for the race
+ * checker that the reference's development relies on (compute-sanitizer). */
+int spork_gemm_sm100_ring_model(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k,
+                                int max_ctas, int sm_count, int stages, int skew, uint32_t seed, uint32_t group,
+                                int inject, uint64_t* stats);
+
+/* Tracing of the 256 x 512 kernel: later launches make their first CTA write SM
+ * clock stamps (clock64) of its tile hand-overs into `device_buffer`, eight
+ * 64-bit values per work item of that CTA, for the first `items` work items:
+ * [0], [1] the issuer found accumulator half 0 / 1 free; [2], [3], [4] half 0 was
+ * final, sat in the epilogue's registers, had its last store issued; [5], [6], [7]
+ * the same for half 1.  The buffer must stay valid until tracing is switched off
+ * with (NULL, 0).  Process-wide, like the tuning knobs.  No counterpart in the
+ * reference (its tracing is nvtx ranges and event timing, gemm/gemm_test.cu). */
+int spork_gemm_sm100_trace(void* device_buffer, uint32_t items);
 
 /* The knobs as later launches will see them: out[0] = ring depth, [1] = raster
  * group, [2] = the L2 hint bits a launch carries (bit 0 = A evict-last, bit 1 = B
  * evict-last, bit 2 = B evict-first; 0 = none), [3] = poll back-off, [4] =
  * experiment bits, [5] = column blocks per stage, [6] = 256 x 512 tile choice,
- * [7] = its skew, [8] = its raster group.  No counterpart in the reference. */
+ * [7] = its skew, [8] = its raster group, [9] = 1 if launches are not programmatic
+ * dependents.  capacity >= 10.  No counterpart in the reference. */
 int spork_gemm_sm100_tuning(int* out, int capacity);
 
 /* Host-only view of how a launch would be laid out (no CUDA call; usable without a

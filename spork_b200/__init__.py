@@ -29,6 +29,8 @@ from .api import (  # noqa: F401
     matmul_sm100_supports,
     matmul_sm100_tf32,
     status,
+    ring_model,
+    trace,
     tune,
     tuning,
     version,

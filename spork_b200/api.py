@@ -75,6 +75,11 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_last_clock_mhz.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
         L.spork_gemm_sm100_tune.restype = i32
+        L.spork_gemm_sm100_ring_model.argtypes = [u32, u32, u32, i32, i32, i32, i32, i32, i32, i32, u32, u32, i32,
+                                                  ctypes.POINTER(ctypes.c_uint64)]
+        L.spork_gemm_sm100_ring_model.restype = i32
+        L.spork_gemm_sm100_trace.argtypes = [vp, u32]
+        L.spork_gemm_sm100_trace.restype = i32
         L.spork_gemm_sm100_tuning.argtypes = [ctypes.POINTER(i32), i32]
         L.spork_gemm_sm100_tuning.restype = i32
         L.spork_gemm_sm100_status.argtypes = [vp, ctypes.POINTER(u32)]
@@ -232,20 +237,48 @@ def last_clock_mhz(stream=None) -> float:
 
 
 def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0, *, experiment: int = 0,
-         k_atoms: int = 0, wide: int = 0, wide_skew: int = 0, wide_group_m: int = 0) -> None:
+         k_atoms: int = 0, wide: int = 0, wide_skew: int = 0, wide_group_m: int = 0,
+         no_early_launch: bool = False) -> None:
     """Process-wide tuning knobs of later GEMM launches (see spork_gemm_sm100_tune in the header).
 
     ``l2_hints`` may carry the packed upper bits itself (the C form); the keyword arguments are OR-ed in."""
-    packed = l2_hints | ((experiment & 7) << 4) | ((k_atoms & 3) << 8) | ((wide & 3) << 10) | \
-        ((wide_skew & 15) << 12) | ((wide_group_m & 255) << 16)
+    packed = l2_hints | ((experiment & 15) << 4) | ((k_atoms & 3) << 8) | ((wide & 3) << 10) | \
+        ((wide_skew & 15) << 12) | ((wide_group_m & 255) << 16) | (int(bool(no_early_launch)) << 24)
     _check(lib().spork_gemm_sm100_tune(stages, group_m, packed, backoff_ns), "spork_gemm_sm100_tune")
+
+
+def ring_model(M: int, N: int, K: int, *, block_n: int = 256, cta_group: int = 2, split_k: int = 1, max_ctas: int = 0,
+               sm_count: int = 148, stages: int | None = None, skew: int = 4, seed: int = 0, group: int = 0,
+               inject: int = 0):
+    """Run the host-side model of the kernels' barrier protocol for one CTA group of a launch plan
+    (spork_gemm_sm100_ring_model); returns (code, stats) with code 0 = every invariant held."""
+    if stages is None:
+        stages = 4 if block_n == 512 else 6
+    stats = (ctypes.c_uint64 * 4)()
+    rc = lib().spork_gemm_sm100_ring_model(M, N, K, block_n, cta_group, split_k, max_ctas, sm_count, stages, skew, seed,
+                                           group, inject, stats)
+    return rc, {"items": int(stats[0]), "mma_ops": int(stats[1]), "steps": int(stats[2]), "groups": int(stats[3])}
+
+
+def trace(buffer=None) -> None:
+    """Switch the tile hand-over trace of the 256 x 512 kernel on (``buffer``: an int64 CUDA tensor of
+    8 * items elements that outlives the traced launches) or off (None).  See spork_gemm_sm100_trace."""
+    import torch
+
+    if buffer is None:
+        _check(lib().spork_gemm_sm100_trace(None, 0), "spork_gemm_sm100_trace")
+        return
+    if not buffer.is_cuda or buffer.dtype != torch.int64 or not buffer.is_contiguous() or buffer.numel() < 8:
+        raise TypeError("the trace buffer must be a contiguous int64 CUDA tensor of at least 8 elements")
+    _check(lib().spork_gemm_sm100_trace(int(buffer.data_ptr()), buffer.numel() // 8), "spork_gemm_sm100_trace")
 
 
 def tuning() -> dict:
     """The knobs as the next launch will see them (``l2_hints`` is the effective hint mask)."""
-    out = (ctypes.c_int * 9)()
-    _check(lib().spork_gemm_sm100_tuning(out, 9), "spork_gemm_sm100_tuning")
-    keys = ("stages", "group_m", "l2_hints", "backoff_ns", "experiment", "k_atoms", "wide", "wide_skew", "wide_group_m")
+    out = (ctypes.c_int * 10)()
+    _check(lib().spork_gemm_sm100_tuning(out, 10), "spork_gemm_sm100_tuning")
+    keys = ("stages", "group_m", "l2_hints", "backoff_ns", "experiment", "k_atoms", "wide", "wide_skew", "wide_group_m",
+            "no_early_launch")
     return dict(zip(keys, (int(v) for v in out)))
 
 

@@ -18,7 +18,8 @@ FLAGS = [
 
 
 def sources() -> list[str]:
-    return sorted(p for p in glob.glob(os.path.join(CSRC, "*.cu")) if not os.path.basename(p).startswith("main_"))
+    found = glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp"))
+    return sorted(p for p in found if not os.path.basename(p).startswith("main_"))
 
 
 def _stale(target: str, deps: list[str]) -> bool:
@@ -37,7 +38,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = []
     procs = []
     for src in sources():
-        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(objdir, os.path.splitext(os.path.basename(src))[0] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
             cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]

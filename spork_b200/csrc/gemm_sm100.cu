@@ -37,6 +37,7 @@
 
 #include "../../include/spork_b200.h"
 #include "device_state.h"
+#include "gemm_plan.h"
 #include "ptx_sm100.cuh"
 
 namespace spork {
@@ -85,31 +86,6 @@ struct Config {
     static_assert(kUmmaN % 16 == 0 && kUmmaN >= 16 && kUmmaN <= 256, "UMMA N");
 };
 
-struct Params {
-    uint32_t M, N, K;
-    uint32_t tiles_m, tiles_n;   // output tiles (tile = kBlockM*CG x BLOCK_N)
-    uint32_t split_k;            // >= 1
-    uint32_t batches;            // >= 1: independent problems A[l] * B[l]^T -> C[l], contiguous in memory
-    uint32_t kb_per_split;       // K blocks per split
-    uint32_t num_kb;             // ceil(K / kBlockK)
-    uint32_t use_tma_store;      // 0: guarded scalar stores (N % 4 != 0)
-    uint32_t stages;             // ring depth in use (<= Config::kStages)
-    uint32_t group_m;            // raster: m-tiles per group
-    uint32_t l2_hints;           // bit 0: A loads evict_last, bit 1: B loads evict_last, bit 2: B loads evict_first
-    uint32_t backoff_ns;         // sleep between polls of the long (epilogue / producer) waits; 0 = spin
-    // stream-K: the last `sk_tiles` tiles (raster order) are cut along K into one contiguous share of
-    // K blocks per CTA group and reduce-added into a zeroed C; the first `dp_tiles` run whole.
-    uint32_t dp_tiles, sk_tiles;
-    uint32_t sk_share, sk_extra; // group g owns sk_share (+1 if g < sk_extra) K blocks of the stream-K part
-    uint32_t wide_skew;          // 256 x 512 tiles: K blocks of one accumulator half issued ahead of the other at both
-                                 // ends of a tile (1 .. ring depth)
-    uint32_t experiment;         // diagnostics only, results undefined: bit 0 = epilogue drops its stores,
-                                 // bit 1 = producer stops issuing loads once the ring has been filled once,
-                                 // bit 2 = epilogue stores straight from registers (no shared-memory staging)
-    float* C;
-    uint32_t* status;            // device status word
-};
-
 struct Barriers {
     uint64_t full[8];
     uint64_t empty[8];
@@ -118,86 +94,6 @@ struct Barriers {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-
-struct WorkItem {
-    uint32_t m_tile, n_tile, kb_begin, kb_end, split, batch;
-    bool reduce;  // the partial tile is added into C instead of stored
-};
-
-// Grouped raster (the superblock idea of gemm/gemm_sm90.cu:318-345): work items
-// that run at the same time cover kGroupM m-tiles by a run of n-tiles; the groups
-// alternate their direction along n.
-__host__ __device__ __forceinline__ void decode_tile(const Params& p, uint32_t t, WorkItem& w)
-{
-    const uint32_t group_size = p.group_m * p.tiles_n;
-    const uint32_t g = t / group_size;
-    const uint32_t first_m = g * p.group_m;
-    const uint32_t gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
-    const uint32_t r = t % group_size;
-    w.m_tile = first_m + r % gm;
-    w.n_tile = r / gm;
-    // every other group walks the n-tiles backwards: the B strips the previous group touched last are the
-    // first to be used again while they are still in L2 (+0.5 % at 8192^3 with the part at its power cap)
-    if (g & 1u) {
-        w.n_tile = p.tiles_n - 1u - w.n_tile;
-    }
-}
-
-// Work of CTA group `g` of `G`.  Without stream-K: items g, g+G, ... of the (split, tile) list.  With
-// stream-K: first the whole tiles g, g+G, ... < dp_tiles, then this group's share of the K blocks of the
-// remaining tiles, which touches one or a few consecutive tiles.
-__host__ __device__ __forceinline__ uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
-{
-    if (p.sk_tiles == 0) {
-        const uint32_t items = p.tiles_m * p.tiles_n * p.split_k * p.batches;
-        return items > g ? (items - g - 1) / G + 1 : 0;
-    }
-    const uint32_t n1 = p.dp_tiles / G;  // dp_tiles is a multiple of G
-    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-    if (cnt == 0) {
-        return n1;
-    }
-    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-    return n1 + ((u0 + cnt - 1) / p.num_kb - u0 / p.num_kb + 1);
-}
-
-__host__ __device__ __forceinline__ WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i)
-{
-    WorkItem w;
-    if (p.sk_tiles == 0) {
-        const uint32_t item = g + i * G;
-        const uint32_t tiles = p.tiles_m * p.tiles_n;
-        const uint32_t q = item / tiles;   // (batch, split), split fastest
-        w.batch = q / p.split_k;
-        w.split = q % p.split_k;
-        decode_tile(p, item % tiles, w);
-        w.kb_begin = w.split * p.kb_per_split;
-        const uint32_t e = w.kb_begin + p.kb_per_split;
-        w.kb_end = e < p.num_kb ? e : p.num_kb;
-        w.reduce = p.split_k > 1;
-        return w;
-    }
-    w.split = 0;
-    w.batch = 0;   // stream-K is never planned for a batch
-    const uint32_t n1 = p.dp_tiles / G;
-    if (i < n1) {
-        decode_tile(p, g + i * G, w);
-        w.kb_begin = 0;
-        w.kb_end = p.num_kb;
-        w.reduce = false;
-        return w;
-    }
-    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-    const uint32_t rel = u0 / p.num_kb + (i - n1);   // tile index inside the stream-K part
-    const uint32_t t0 = rel * p.num_kb;              // its first K-block unit
-    decode_tile(p, p.dp_tiles + rel, w);
-    w.kb_begin = u0 > t0 ? u0 - t0 : 0;
-    const uint32_t u1 = u0 + cnt;
-    w.kb_end = u1 < t0 + p.num_kb ? u1 - t0 : p.num_kb;
-    w.reduce = true;
-    return w;
-}
 
 __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_t* abort_flag, uint32_t role,
                                                uint32_t where)
@@ -235,10 +131,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // Clock probe: CTA 0 notes SM cycles and wall-clock nanoseconds at both ends of the launch; their
     // ratio is the SM clock the kernel really ran at (the power cap moves it far below the nominal clock).
     unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
-    if (!kWorkspace && blockIdx.x == 0 && threadIdx.x == 0) {
-        probe[0] = (unsigned long long)clock64();
-        probe[1] = global_timer_ns();
-    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
@@ -269,6 +161,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+
+    // Everything above is independent of earlier work in the stream.  When launched as a programmatic
+    // dependent, this CTA may have been set up while the previous kernel was still running on other SMs;
+    // from here on it reads and writes global memory, so the previous kernel must be complete.  The next
+    // launch may set itself up in the same way while this one runs.
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (!kWorkspace && blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
 
     const uint32_t num_items = group_item_count(p, group_id, num_groups);  // this CTA group's work items
     constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;  // elements along K per stage
@@ -528,7 +431,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
         }
         if (lane == 0) {
-            bulk_wait_group<0>();
+            // shared memory must outlive the stores' reads of it; their writes are complete when the kernel is
+            bulk_wait_group_read<0>();
         }
     }
 
@@ -631,93 +535,6 @@ static int make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
-// split_k = 0 ("choose"): a problem with fewer output tiles than CTA groups and a long K leaves SMs idle;
-// cutting K into s ranges turns it into tiles * s work items.  Pick the s (1..16, at least 8 K blocks per
-// range) with the smallest modelled time: waves(s) * (K blocks per range * cycles per block + epilogue),
-// where a reduce-add epilogue is dearer than a store.  Only for 256-wide tiles: narrower ones are chosen
-// for problems that are bound by memory, where this model does not hold.  Pure arithmetic.
-static uint32_t choose_split(uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m, uint32_t block_n, uint32_t cta_group,
-                             uint32_t elems_k, int max_ctas, int sm_count, uint32_t batches)
-{
-    const uint64_t tiles = (uint64_t)((M + tile_m - 1) / tile_m) * ((N + block_n - 1) / block_n) * (batches ? batches : 1);
-    const uint32_t num_kb = (K + elems_k - 1) / elems_k;
-    uint32_t groups = (uint32_t)(sm_count / (int)cta_group);
-    if (max_ctas > 0 && (uint32_t)max_ctas / cta_group < groups) {
-        groups = (uint32_t)max_ctas / cta_group;
-    }
-    if (block_n != 256 || groups == 0 || tiles >= groups || num_kb < 16) {
-        return 1;
-    }
-    const uint64_t cycles_per_kb = 512, epilogue_store = 4000, epilogue_reduce = 6000;
-    uint32_t best = 1;
-    uint64_t best_time = (uint64_t)num_kb * cycles_per_kb + epilogue_store;  // one wave, s = 1
-    for (uint32_t s = 2; s <= 16; ++s) {
-        const uint32_t kb_per = (num_kb + s - 1) / s;
-        if (kb_per < 8) {
-            break;
-        }
-        const uint32_t splits = (num_kb + kb_per - 1) / kb_per;  // no empty ranges
-        const uint64_t items = tiles * splits;
-        const uint64_t waves = (items + groups - 1) / groups;
-        const uint64_t t = waves * ((uint64_t)kb_per * cycles_per_kb + epilogue_reduce);
-        if (t < best_time) {
-            best_time = t;
-            best = splits;
-        }
-    }
-    return best;
-}
-
-// Host-side launch plan: tile grid, K split, number of CTA groups and the stream-K partition.  Pure
-// arithmetic (no CUDA call), shared by the launch paths and by spork_gemm_sm100_plan.
-static void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uint32_t K, uint32_t tile_m,
-                        uint32_t block_n, uint32_t cta_group, uint32_t elems_k, uint32_t split_k, bool stream_k,
-                        int max_ctas, int sm_count, uint32_t batches = 1)
-{
-    p.batches = batches < 1 ? 1 : batches;
-    if (p.batches > 1) {
-        stream_k = false;
-    }
-    p.M = M;
-    p.N = N;
-    p.K = K;
-    p.tiles_m = (M + tile_m - 1) / tile_m;
-    p.tiles_n = (N + block_n - 1) / block_n;
-    p.num_kb = (K + elems_k - 1) / elems_k;
-    if (split_k > p.num_kb) {
-        split_k = p.num_kb;
-    }
-    if (split_k < 1) {
-        split_k = 1;
-    }
-    p.kb_per_split = (p.num_kb + split_k - 1) / split_k;
-    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
-    p.use_tma_store = (N % 4 == 0) ? 1u : 0u;
-    p.dp_tiles = 0;
-    p.sk_tiles = 0;
-    p.sk_share = 0;
-    p.sk_extra = 0;
-    const uint64_t items = (uint64_t)p.tiles_m * p.tiles_n * p.split_k * p.batches;
-    groups = (uint32_t)(sm_count / (int)cta_group);
-    if (max_ctas > 0 && (uint32_t)max_ctas / cta_group < groups) {
-        groups = (uint32_t)max_ctas / cta_group;
-    }
-    if (groups == 0) {
-        groups = 1;
-    }
-    const uint32_t tiles = p.tiles_m * p.tiles_n;
-    if (stream_k && p.split_k == 1 && tiles % groups != 0) {
-        // whole waves run tile by tile; the K blocks of the last partial wave are dealt out evenly
-        p.dp_tiles = tiles / groups * groups;
-        p.sk_tiles = tiles - p.dp_tiles;
-        const uint64_t units = (uint64_t)p.sk_tiles * p.num_kb;
-        p.sk_share = (uint32_t)(units / groups);
-        p.sk_extra = (uint32_t)(units % groups);
-    } else if (items < groups) {
-        groups = (uint32_t)items;
-    }
-}
-
 // Process-wide tuning knobs (spork_gemm_sm100_tune); the defaults are the measured best.
 struct Tuning {
     int stages = 0;       // 0 = as deep as shared memory allows
@@ -729,6 +546,9 @@ struct Tuning {
     int wide = 0;         // 256 x 512 tiles: 0 = choose, 1 = never, 2 = whenever the shape allows
     int wide_skew = 0;    // 0 = default (ring depth)
     int wide_group_m = 0; // 0 = default raster group of the 256 x 512 kernel
+    int no_early_launch = 0;  // 1: launches are not programmatic dependents (no overlap with the previous kernel's tail)
+    unsigned long long* trace = nullptr;  // spork_gemm_sm100_trace
+    uint32_t trace_items = 0;
 };
 static Tuning g_tuning;
 
@@ -821,13 +641,16 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     cfg.blockDim = dim3(kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CG;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // the kernel sets itself up before it waits for the previous kernel in the stream (see grid_dependency_wait)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tune.no_early_launch ? 1 : 2;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, tmap_c, p);
     return (int)e;
 }
@@ -863,8 +686,10 @@ static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const 
     p.group_m = tune.wide_group_m >= 1 ? (uint32_t)tune.wide_group_m : (uint32_t)kWideGroupM;
     p.l2_hints = effective_l2_hints(tune.l2_hints);
     p.backoff_ns = (uint32_t)tune.backoff_ns;
-    p.experiment = (uint32_t)tune.experiment & 1u;
+    p.experiment = (uint32_t)tune.experiment & 9u;
     p.wide_skew = tune.wide_skew >= 1 ? (uint32_t)tune.wide_skew : (uint32_t)kWideStages;
+    p.trace = tune.trace;
+    p.trace_items = tune.trace_items;
 
     CUtensorMap tmap_a, tmap_b, tmap_c;
     int rc = make_tmap_2d(&tmap_a, kOperandType, kOperandBytes, A, M, K, kBlockM, kElemsK);
@@ -894,13 +719,15 @@ static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const 
     cfg.blockDim = dim3(kWideThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tune.no_early_launch ? 1 : 2;
     return (int)cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, tmap_c, p);
 }
 
@@ -1364,15 +1191,16 @@ extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0xFFFFFF || ((l2_hints >> 8) & 3) > 2 ||
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x1FFFFFF || ((l2_hints >> 8) & 3) > 2 ||
         ((l2_hints >> 10) & 3) > 2 || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
-    spork::gemm_sm100::g_tuning.experiment = (l2_hints >> 4) & 7;  // bits 4..6: diagnostic experiments (see Params)
+    spork::gemm_sm100::g_tuning.experiment = (l2_hints >> 4) & 15; // bits 4..7: diagnostic experiments (see Params)
     spork::gemm_sm100::g_tuning.k_atoms = (l2_hints >> 8) & 3;     // bits 8..9: column blocks per stage, 0 = choose
     spork::gemm_sm100::g_tuning.wide = (l2_hints >> 10) & 3;       // bits 10..11: 256 x 512 tiles: choose / never / always
     spork::gemm_sm100::g_tuning.wide_skew = (l2_hints >> 12) & 15; // bits 12..15: their skew, 0 = default
     spork::gemm_sm100::g_tuning.wide_group_m = (l2_hints >> 16) & 255;  // bits 16..23: their raster group, 0 = default
+    spork::gemm_sm100::g_tuning.no_early_launch = (l2_hints >> 24) & 1; // bit 24: plain stream order, no early set-up
     l2_hints &= 15;   // bit 3 = "no hints at all" must survive (see effective_l2_hints)
     spork::gemm_sm100::g_tuning.stages = stages;
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
@@ -1381,15 +1209,25 @@ extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int 
     return 0;
 }
 
+extern "C" int spork_gemm_sm100_trace(void* device_buffer, uint32_t items)
+{
+    if ((device_buffer == nullptr) != (items == 0) || (reinterpret_cast<uintptr_t>(device_buffer) & 7u)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::gemm_sm100::g_tuning.trace = static_cast<unsigned long long*>(device_buffer);
+    spork::gemm_sm100::g_tuning.trace_items = items;
+    return 0;
+}
+
 extern "C" int spork_gemm_sm100_tuning(int* out, int capacity)
 {
-    if (!out || capacity < 9) {
+    if (!out || capacity < 10) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     const spork::gemm_sm100::Tuning t = spork::gemm_sm100::g_tuning;
-    const int vals[9] = {t.stages, t.group_m, (int)spork::gemm_sm100::effective_l2_hints(t.l2_hints), t.backoff_ns,
-                         t.experiment, t.k_atoms, t.wide, t.wide_skew, t.wide_group_m};
-    for (int i = 0; i < 9; ++i) {
+    const int vals[10] = {t.stages, t.group_m, (int)spork::gemm_sm100::effective_l2_hints(t.l2_hints), t.backoff_ns,
+                          t.experiment, t.k_atoms, t.wide, t.wide_skew, t.wide_group_m, t.no_early_launch};
+    for (int i = 0; i < 10; ++i) {
         out[i] = vals[i];
     }
     return 0;

@@ -15,9 +15,10 @@
 // ring depth (4 stages of 48 KB).
 //
 // The epilogue warps (8) copy a half accumulator from tensor memory into registers in one go
-// (128 fp32 per thread), release the columns at once, and only then write the registers out
-// through a swizzled shared-memory slab and TMA stores: the tensor pipe waits for the copy into
-// registers, not for the stores.
+// (128 fp32 per thread), release the columns at once, and only then write the registers out: the
+// tensor pipe waits for the copy into registers, not for the stores.  The registers of one half must
+// be out before the other half can be taken, so the write-out (a swizzled shared-memory slab per warp
+// and TMA stores) is on the critical path at the tile ends.
 //
 // Same operand layout, tensor maps, work-item list, raster and bounded waits as gemm_kernel.
 #pragma once
@@ -52,19 +53,6 @@ struct WideBarriers {
     uint32_t abort_flag;
 };
 
-// Sizes of the chunks a tile's K-blocks are issued in.  Inside a chunk the MMAs of H0 come first, then
-// those of H1.  The first and the last chunk are `skew` K-blocks long (shorter tiles are cut in two, or
-// run as one chunk), the ones between are single K-blocks.  Pure arithmetic, shared with the host-side
-// model of the schedule.
-__host__ __device__ __forceinline__ uint32_t wide_chunk(uint32_t n, uint32_t done, uint32_t skew)
-{
-    const uint32_t rem = n - done;
-    if (done == 0) {
-        return n >= 2 * skew ? skew : (n > skew ? n - n / 2 : n);
-    }
-    return rem <= skew ? rem : 1u;
-}
-
 template <bool kTf32>
 __global__ void __launch_bounds__(kWideThreads, 1)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -89,10 +77,6 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        probe[0] = (unsigned long long)clock64();
-        probe[1] = global_timer_ns();
-    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWideStages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
@@ -120,6 +104,15 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     cluster_wait_acquire();
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+
+    // set-up done: from here on global memory is touched, so the previous kernel in the stream must be
+    // complete (see gemm_kernel)
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
 
     const uint32_t num_items = group_item_count(p, group_id, num_groups);
     constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
@@ -172,6 +165,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bool ok = true;
             for (uint32_t item = 0; item < num_items && ok; ++item) {
                 const WorkItem w = group_item(p, group_id, num_groups, item);
+                const bool tracing = p.trace != nullptr && blockIdx.x == 0 && item < p.trace_items;
                 const uint32_t n = w.kb_end - w.kb_begin;
                 const uint32_t tile_phase = item & 1u;
                 uint32_t done = 0;
@@ -192,6 +186,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                 break;
                             }
                             tcgen05_fence_after();
+                        }
+                        if (first && tracing && elected) {
+                            p.trace[8 * item + h] = (unsigned long long)clock64();  // [0], [1]: this half was free
                         }
                         const uint32_t tmem_d = tmem_base + h * kWideHalfN;
                         uint32_t s = stage, ph = phase;
@@ -260,6 +257,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t tile_phase = item & 1u;
             const uint32_t row0 = w.m_tile * (kBlockM * CG) + cta_rank * kBlockM + quarter * 32;
             const bool rows_live = row0 < p.M && w.kb_begin < w.kb_end;
+            const bool tracing = p.trace != nullptr && blockIdx.x == 0 && warp == kEpilogueWarp0 && lane == 0 &&
+                                 item < p.trace_items;
 #pragma unroll 1
             for (uint32_t h = 0; h < 2; ++h) {
                 if (!mbar_wait(smem_u32(&bars->tmem_full[h]), tile_phase, abort_flag, p.backoff_ns)) {
@@ -270,6 +269,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     break;
                 }
                 tcgen05_fence_after();
+                if (tracing) {
+                    p.trace[8 * item + 2 + 3 * h] = (unsigned long long)clock64();  // [2], [5]: the half was final
+                }
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + h * kWideHalfN + part * 128u;
                 uint32_t r[4][32];
 #pragma unroll
@@ -283,6 +285,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (lane == 0) {
                     mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[h]), 0));
                 }
+                if (tracing) {
+                    p.trace[8 * item + 3 + 3 * h] = (unsigned long long)clock64();  // [3], [6]: it sits in registers
+                }
                 const uint32_t col0 = w.n_tile * kWideN + h * kWideHalfN + part * 128u;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -290,7 +295,31 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (!rows_live || col >= p.N || (p.experiment & 1u)) {
                         continue;  // warp-uniform
                     }
-                    if (p.use_tma_store) {
+                    if (p.use_tma_store && !w.reduce && (p.experiment & 8u)) {
+                        // Diagnostic alternative to the TMA stores below (same results): plain stores, made
+                        // whole 128-byte lines by a turn through the slab.  Eight lanes write one row of the
+                        // slab (128 bytes), four rows per instruction.  Measured slower than the TMA stores
+                        // on every shape, at the power limit and off it.
+                        __syncwarp();
+                        const uint32_t row_addr = slab + lane * 128u;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
+                                         r[c][4 * j + 2], r[c][4 * j + 3]);
+                        }
+                        __syncwarp();
+                        const uint32_t sub_row = lane >> 3, piece = lane & 7u;
+                        const uint32_t gcol = col + piece * 4u;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t srow = 4u * i + sub_row;
+                            const uint4 v = ld_shared_v4(slab + srow * 128u + ((piece ^ (srow & 7u)) << 4));
+                            const uint32_t grow = row0 + srow;
+                            if (grow < p.M && gcol < p.N) {
+                                st_global_v4(p.C + (size_t)grow * p.N + gcol, v);
+                            }
+                        }
+                    } else if (p.use_tma_store) {
                         if (lane == 0) {
                             bulk_wait_group_read<0>();  // the previous store has read the slab
                         }
@@ -328,10 +357,14 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     }
                 }
+                if (tracing) {
+                    p.trace[8 * item + 4 + 3 * h] = (unsigned long long)clock64();  // [4], [7]: its last store was issued
+                }
             }
         }
         if (lane == 0) {
-            bulk_wait_group<0>();
+            // shared memory must outlive the stores' reads of it; their writes are complete when the kernel is
+            bulk_wait_group_read<0>();
         }
     }
 

@@ -7,7 +7,15 @@
 // Unlike the reference, a mismatch or a device-side time-out makes the exit
 // status non-zero.
 //
-//   gemm [--quick] [--json FILE]
+//   gemm [--quick] [--json FILE] [--config headline|reference|all] [--algos NAME[,NAME...]]
+//        [--shape M,N,K[,STYLE]] [--device D]
+//
+//   --config   which shape list runs: the benchmark's own configurations, the reference's list
+//              (gemm/gemm_main.cpp:98-122, wave-quantisation probes included), or both (default)
+//   --algos    restrict the algorithm columns by name prefix (cublas, baseline, mine, mine_wide, n128, n64,
+//              split_k, stream_k, auto_k)
+//   --shape    run one shape instead of a list; STYLE 0..3 as gemm/gemm_main.cpp:81-95, 4 = uniform [-1,1)
+//   --device   CUDA device ordinal (one harness process per GPU)
 #include <cublas_v2.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,8 +40,9 @@ enum class AlgorithmCode {
     mine_sm_100_split_k,
     mine_sm_100_stream_k,
     mine_sm_100_auto_k,
+    mine_sm_100_wide,
 };
-constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_auto_k);
+constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_wide);
 
 inline uint32_t algorithm_code_bit(AlgorithmCode code) { return 1u << static_cast<uint32_t>(code); }
 
@@ -48,8 +57,26 @@ inline const char* algorithm_name(AlgorithmCode code)
     case AlgorithmCode::mine_sm_100_split_k: return "mine_sm_100 (split k)";
     case AlgorithmCode::mine_sm_100_stream_k: return "mine_sm_100 (stream k)";
     case AlgorithmCode::mine_sm_100_auto_k: return "mine_sm_100 (automatic k)";
+    case AlgorithmCode::mine_sm_100_wide: return "mine_sm_100 (256x512 tiles)";
     }
     return "unknown";
+}
+
+// Short names for --algos.
+inline const char* algorithm_key(AlgorithmCode code)
+{
+    switch (code) {
+    case AlgorithmCode::cublas_f16: return "cublas";
+    case AlgorithmCode::baseline_f16: return "baseline";
+    case AlgorithmCode::mine_sm_100: return "mine";
+    case AlgorithmCode::mine_sm_100_n128: return "n128";
+    case AlgorithmCode::mine_sm_100_n64: return "n64";
+    case AlgorithmCode::mine_sm_100_split_k: return "split_k";
+    case AlgorithmCode::mine_sm_100_stream_k: return "stream_k";
+    case AlgorithmCode::mine_sm_100_auto_k: return "auto_k";
+    case AlgorithmCode::mine_sm_100_wide: return "mine_wide";
+    }
+    return "";
 }
 
 struct TestParams {
@@ -60,6 +87,7 @@ struct TestParams {
 
 static int g_failures = 0;
 static FILE* g_json = nullptr;
+static uint32_t g_algorithm_mask = ~0u;  // --algos
 
 #define CUDA_OK(x)                                                                                   \
     do {                                                                                             \
@@ -69,6 +97,40 @@ static FILE* g_json = nullptr;
             exit(1);                                                                                 \
         }                                                                                            \
     } while (0)
+
+// What the reference prints at the first wrong element (gemm/gemm_test.cu:100-120,157-175): the pair
+// [expected, got] for the element and its neighbours two rows and columns around, the element itself in
+// bold.  Done on the host here: the few rows involved are copied back.
+static void print_neighbourhood(const float* d_expected, const float* d_got, uint32_t rows, uint32_t cols, uint32_t y,
+                                uint32_t x)
+{
+    if (y >= rows || x >= cols) {
+        return;
+    }
+    const uint32_t y0 = y < 2 ? 0u : y - 2, y1 = y + 2 >= rows ? rows - 1u : y + 2;
+    const uint32_t x0 = x < 2 ? 0u : x - 2, x1 = x + 2 >= cols ? cols - 1u : x + 2;
+    const uint32_t h = y1 - y0 + 1, w = x1 - x0 + 1;
+    std::vector<float> e(size_t(h) * w), g(size_t(h) * w);
+    const size_t pitch = size_t(cols) * sizeof(float);
+    const size_t origin = size_t(y0) * cols + x0;
+    if (cudaMemcpy2D(e.data(), w * sizeof(float), d_expected + origin, pitch, w * sizeof(float), h,
+                     cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy2D(g.data(), w * sizeof(float), d_got + origin, pitch, w * sizeof(float), h,
+                     cudaMemcpyDeviceToHost) != cudaSuccess) {
+        return;
+    }
+    printf("  [%u,%u] expected %g, got %g; rows %u..%u, columns %u..%u as [expected, got]:\n", y, x,
+           e[size_t(y - y0) * w + (x - x0)], g[size_t(y - y0) * w + (x - x0)], y0, y1, x0, x1);
+    for (uint32_t r = 0; r < h; ++r) {
+        printf("  ");
+        for (uint32_t c = 0; c < w; ++c) {
+            const bool here = y0 + r == y && x0 + c == x;
+            printf("%s[%6g, %6g]%s  ", here ? "\x1b[1m" : "", e[size_t(r) * w + c], g[size_t(r) * w + c],
+                   here ? "\x1b[0m" : "");
+        }
+        printf("\n");
+    }
+}
 
 static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cublasH)
 {
@@ -99,7 +161,7 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
     const double denom = max_abs(params.test_data_code_A) * max_abs(params.test_data_code_B) * double(params.K) / 1024.0;
 
     for (uint32_t bit_index = 0; bit_index < algorithm_count; ++bit_index) {
-        if ((params.algorithm_code_bits >> bit_index & 1) == 0) {
+        if (((params.algorithm_code_bits & g_algorithm_mask) >> bit_index & 1) == 0) {
             continue;
         }
         const AlgorithmCode algo = static_cast<AlgorithmCode>(bit_index);
@@ -144,6 +206,9 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
             case AlgorithmCode::mine_sm_100_auto_k:
                 launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::automatic);
                 break;
+            case AlgorithmCode::mine_sm_100_wide:
+                launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::output_stationary, 1, 512);
+                break;
             }
             CUDA_OK(cudaEventRecord(test_events[test_i + 1], stream));
         }
@@ -166,6 +231,9 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
                 printf(" first bad [%u,%u]", uint32_t(cmp[0] >> 32), uint32_t(cmp[0]));
             }
             printf("\n");
+            if (!ratio_ok) {
+                print_neighbourhood(d_c_baseline, d_c_tested, params.M, params.N, uint32_t(cmp[0] >> 32), uint32_t(cmp[0]));
+            }
         }
         for (uint32_t test_i = 0; test_i < test_count; ++test_i) {
             CUDA_OK(cudaEventElapsedTime(&test_times[test_i], test_events[test_i], test_events[test_i + 1]));
@@ -203,16 +271,55 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
 int main(int argc, char** argv)
 {
     bool quick = false;
+    const char* config = "all";
+    int device = 0;
+    uint32_t one_shape[4] = {0, 0, 0, 4};
+    bool have_shape = false;
     for (int i = 1; i < argc; ++i) {
         if (!strcmp(argv[i], "--quick")) {
             quick = true;
         } else if (!strcmp(argv[i], "--json") && i + 1 < argc) {
             g_json = fopen(argv[++i], "w");
+        } else if (!strcmp(argv[i], "--config") && i + 1 < argc) {
+            config = argv[++i];
+            if (strcmp(config, "headline") && strcmp(config, "reference") && strcmp(config, "all")) {
+                fprintf(stderr, "--config takes headline, reference or all\n");
+                return 2;
+            }
+        } else if (!strcmp(argv[i], "--device") && i + 1 < argc) {
+            device = atoi(argv[++i]);
+        } else if (!strcmp(argv[i], "--shape") && i + 1 < argc) {
+            const int got = sscanf(argv[++i], "%u,%u,%u,%u", &one_shape[0], &one_shape[1], &one_shape[2], &one_shape[3]);
+            if (got < 3 || one_shape[3] > 4) {
+                fprintf(stderr, "--shape takes M,N,K[,STYLE] with STYLE 0..4\n");
+                return 2;
+            }
+            have_shape = true;
+        } else if (!strcmp(argv[i], "--algos") && i + 1 < argc) {
+            g_algorithm_mask = 0;
+            char* list = argv[++i];
+            for (char* tok = strtok(list, ","); tok; tok = strtok(nullptr, ",")) {
+                bool known = false;
+                for (uint32_t b = 0; b < algorithm_count; ++b) {
+                    if (!strcmp(tok, algorithm_key(static_cast<AlgorithmCode>(b)))) {
+                        g_algorithm_mask |= 1u << b;
+                        known = true;
+                    }
+                }
+                if (!known) {
+                    fprintf(stderr, "--algos: unknown algorithm %s\n", tok);
+                    return 2;
+                }
+            }
+        } else {
+            fprintf(stderr, "usage: gemm [--quick] [--json FILE] [--config headline|reference|all] [--algos LIST] "
+                            "[--shape M,N,K[,STYLE]] [--device D]\n");
+            return 2;
         }
     }
-    CUDA_OK(cudaSetDevice(0));
+    CUDA_OK(cudaSetDevice(device));
     int cc_major = 0;
-    CUDA_OK(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, 0));
+    CUDA_OK(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
     const bool is_b200 = cc_major == 10;
     fprintf(stderr, "is_b200: %i\n", is_b200);
     if (!is_b200) {
@@ -248,6 +355,9 @@ int main(int argc, char** argv)
             if (K >= 4096) {
                 params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_auto_k);
             }
+            if (N >= 1024 && M >= 1024) {
+                params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100_wide);
+            }
         }
         auto run = [&](TestDataCode a, TestDataCode b) {
             params.test_data_code_A = a;
@@ -268,28 +378,45 @@ int main(int argc, char** argv)
         }
     };
 
-    // the configurations of the headline benchmark
-    sized_tests(256, 256, 512, 4);
-    sized_tests(8192, 8192, 8192, 4);
-    for (uint32_t n : {64u, 128u, 256u}) {
-        sized_tests(16384, n, 8192, 4);
-    }
-    // the reference's own shape list (gemm/gemm_main.cpp:98-122)
-    sized_tests(2048, 2048, 2048, 2);
-    sized_tests(768, 768, 32, 2);
-    sized_tests(160, 480, 816, 0);
-    if (!quick) {
-        sized_tests(4096, 4096, 4096, 2);
-        sized_tests(8192, 8192, 8192, 2);
-        sized_tests(7680, 1536, 4096, 0);
-        sized_tests(15360, 1536, 8192, 3);
-        sized_tests(6 * 256, 9 * 256, 65536, 3);
-        sized_tests(32768, 65536, 48, 3);
-        sized_tests(32768, 40016, 816, 0);
-        sized_tests(40016, 32768, 6400, 3);
-        sized_tests(12288, 24576, 1536, 3);
-        sized_tests(6 * 256, 11 * 256, 65536, 3);
-        sized_tests(4 * 256, 11 * 256, 16384 * 3, 3);
+    const bool headline = !strcmp(config, "headline") || !strcmp(config, "all");
+    const bool reference = !strcmp(config, "reference") || !strcmp(config, "all");
+    if (have_shape) {
+        sized_tests(one_shape[0], one_shape[1], one_shape[2], (int)one_shape[3]);
+    } else {
+        if (headline) {
+            // the configurations of the headline benchmark
+            sized_tests(256, 256, 512, 4);
+            sized_tests(8192, 8192, 8192, 4);
+            for (uint32_t n : {64u, 128u, 256u}) {
+                sized_tests(16384, n, 8192, 4);
+            }
+        }
+        if (reference) {
+            // the reference's own shape list (gemm/gemm_main.cpp:98-122)
+            sized_tests(2048, 2048, 2048, 2);
+            sized_tests(768, 768, 32, 2);
+            sized_tests(160, 480, 816, 0);
+        }
+        if (reference && !quick) {
+            sized_tests(4096, 4096, 4096, 2);
+            sized_tests(8192, 8192, 8192, 2);
+            sized_tests(7680, 1536, 4096, 0);
+            sized_tests(15360, 1536, 8192, 3);
+            sized_tests(32768, 65536, 48, 3);
+            sized_tests(32768, 40016, 816, 0);
+            sized_tests(40016, 32768, 6400, 3);
+            sized_tests(12288, 24576, 1536, 3);
+            // wave-quantisation probes (gemm/gemm_main.cpp:104,111-117): n-tile counts either side of what fills
+            // the machine, at a K long enough for K splits to matter
+            for (uint32_t n_tiles : {3u, 9u, 10u, 11u, 12u}) {
+                sized_tests(6 * 256, n_tiles * 256, 65536, 3);
+            }
+            sized_tests(3 * 256, 11 * 256, 65536, 3);
+            sized_tests(9 * 256, 11 * 256, 65536, 3);
+            sized_tests(4 * 256, 11 * 256, 16384 * 3, 3);
+            sized_tests(7680, 3072, 16384, 3);
+            sized_tests(768, 3072, 3072, 3);
+        }
     }
     cudaDeviceSynchronize();
     cublasDestroy(cublasH);

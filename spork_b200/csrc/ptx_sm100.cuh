@@ -71,6 +71,25 @@ __device__ __forceinline__ void cluster_wait_acquire()
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------- programmatic dependent launch ---
+
+// Blocks until every kernel this launch depends on in its stream has completed and its memory
+// operations are visible.  A kernel launched with the "programmatic stream serialization" attribute may
+// begin before its predecessor has finished; everything it does before this instruction must be
+// independent of the predecessor (barrier set-up, tensor-memory allocation, descriptor prefetch).
+// Without that attribute the instruction returns at once.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Tells the runtime that the next kernel in the stream, if it was launched with that attribute, may be
+// scheduled as soon as every CTA of this grid has executed this instruction or exited.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // --------------------------------------------------------------- mbarrier ---
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
@@ -655,6 +674,18 @@ __device__ __forceinline__ void tmem_st_wait()
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_global_v4(void* ptr, uint4 v)
+{
+    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)

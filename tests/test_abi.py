@@ -96,4 +96,4 @@ def test_tuning_knobs_round_trip_without_a_gpu(sp):
     finally:
         sp.tune()
     assert sp.tuning() == {"stages": 0, "group_m": 8, "l2_hints": 3, "backoff_ns": 0, "experiment": 0, "k_atoms": 0,
-                           "wide": 0, "wide_skew": 0, "wide_group_m": 0}
+                           "wide": 0, "wide_skew": 0, "wide_group_m": 0, "no_early_launch": 0}

@@ -300,3 +300,22 @@ def test_headline_size_and_long_sequences(sp, cuda):
             ok, worst = _close(o[h:h + 1].cpu().numpy(), ref.cpu().numpy())
             assert ok, f"{(BH, S, D)} head {h}: max abs error {worst}"
         del q, k, v, o
+
+
+def test_headline_size_heads_against_the_oracle(sp, orc, cuda):
+    """B*H = 256, S = 4096, D = 128 with the configuration's seeds: three heads (first, middle, last) of the
+    full launch against the CPU oracle (8.6 GFLOP per head)."""
+    BH, S, D = 256, 4096, 128
+    q, k, v = _qkv(sp, cuda, BH, S, D, seed=101)
+    o = sp.attn_fwd(q, k, v)
+    sp.status()
+    for h in (0, 131, 255):
+        _, ref = orc.attn_f16(q[h:h + 1].cpu().numpy(), k[h:h + 1].cpu().numpy(), v[h:h + 1].cpu().numpy())
+        ok, worst = _close(o[h:h + 1].cpu().numpy(), ref)
+        assert ok, f"head {h}: max abs error {worst}"
+    # the causal form of the same launch, one head
+    o = sp.attn_fwd(q, k, v, causal=True)
+    sp.status()
+    _, ref = orc.attn_causal_f16(q[77:78].cpu().numpy(), k[77:78].cpu().numpy(), v[77:78].cpu().numpy())
+    ok, worst = _close(o[77:78].cpu().numpy(), ref)
+    assert ok, f"causal head 77: max abs error {worst}"

@@ -361,3 +361,59 @@ def test_automatic_split_k(sp, orc, cuda, M, N, K):
     sp.matmul_sm100(a, b, c, split_k=0)
     sp.status()
     _check(sp, orc, a, b, c, K)
+
+
+@pytest.mark.parametrize("N", [64, 128, 256])
+def test_skinny_configurations_at_their_own_size(sp, orc, cuda, N):
+    """M = 16384, K = 8192, N = 64 / 128 / 256 through the default entry point (the path the benchmark
+    times): CPU-oracle check of row blocks at both edges and in the middle, and the whole result against
+    the CUDA-core comparison kernel."""
+    M, K = 16384, 8192
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    A, B = a.cpu().numpy(), b.cpu().numpy()
+    for m0 in (0, 128, 8192 - 32, M - 64):
+        ref = orc.gemm_f16f32_rows(A, B, m0, 64)
+        assert orc.normalised_error(c[m0:m0 + 64].cpu().numpy(), ref, 1.0, 1.0, K) < 1e-2, (N, m0)
+    base = sp.gemm_baseline(a, b, _poisoned(cuda, M, N))
+    _, max_diff = sp.compare_f32(base, c)
+    assert max_diff / (K * 2.0 ** -10) < 1e-2
+
+
+@pytest.mark.parametrize("no_early_launch", [False, True])
+def test_launches_that_depend_on_the_previous_kernel(sp, orc, cuda, no_early_launch):
+    """A launch may set itself up while the previous kernel in the stream is still finishing, but must not
+    touch memory before that kernel is complete.  A chain in which every product reads what the kernel
+    before it wrote (and overwrites what the one before that read) shows any early access as wrong numbers:
+    c1 = a b^T; a2 = half(c1 / K) by an elementwise kernel; c2 = a2 b^T; then c1 is overwritten by a third
+    product while nothing else separates the launches."""
+    import torch
+
+    M, N, K = 1024, 1024, 1024
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    try:
+        sp.tune(no_early_launch=no_early_launch)
+        with torch.cuda.stream(s):
+            for _ in range(3):  # repeated so that launches really queue up behind one another
+                c1 = _poisoned(cuda, M, N)
+                c2 = _poisoned(cuda, M, N)
+                sp.matmul_sm100(a, b, c1, stream=s)
+                a2 = (c1 * (1.0 / K)).to(torch.float16)
+                sp.matmul_sm100(a2, b, c2, stream=s)
+                keep = c1.clone()
+                sp.matmul_sm100(b, a, c1, stream=s)   # overwrites what the clone and the scaling read
+        sp.status(stream=s)
+    finally:
+        sp.tune()
+    A, B = a.cpu().numpy(), b.cpu().numpy()
+    ref1 = orc.gemm_f16f32(A, B)
+    assert orc.normalised_error(keep.cpu().numpy(), ref1, 1.0, 1.0, K) < 1e-2
+    assert torch.equal(a2, (keep * (1.0 / K)).to(torch.float16))
+    ref2 = orc.gemm_f16f32(a2.cpu().numpy(), B)
+    assert orc.normalised_error(c2.cpu().numpy(), ref2, float(a2.abs().max()), 1.0, K) < 1e-2
+    ref3 = orc.gemm_f16f32(B, A)
+    assert orc.normalised_error(c1.cpu().numpy(), ref3, 1.0, 1.0, K) < 1e-2
