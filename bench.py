@@ -116,6 +116,60 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def pin_to_gpu_numa_node(torch, dev):
+    """Bind this process's threads to the cores of the NUMA node the GPU hangs off, so that the pinned host
+    buffers allocated afterwards (first touch) and the copies' submitting threads are local to the GPU's
+    host link.  Returns what was done, for the JSON line; does nothing where sysfs does not say."""
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"node": None, "note": "no NUMA affinity reported for the GPU"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"node": node, "note": "none of the node's cores is available to this process"}
+        os.sched_setaffinity(0, allowed)
+        return {"node": node, "cores": len(allowed)}
+    except (OSError, ValueError, AttributeError) as e:
+        return {"node": None, "note": f"not pinned: {type(e).__name__}"}
+
+
+def host_link_ceiling(torch, dev, host_in, host_out, barrier, reps=4):
+    """Pinned-memory copies of one step's bytes in both directions at once: what the host link alone allows.
+    `host_in` (fp16 A, also standing for B, which has the same size) goes to the device twice, `host_out`
+    comes back.  Returns GB/s per direction while both run and the seconds one step's bytes take."""
+    d_in = torch.empty_like(host_in, device=dev)
+    d_in2 = torch.empty_like(host_in, device=dev)
+    d_out = torch.empty(host_out.shape, dtype=host_out.dtype, device=dev)
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def both():
+        with torch.cuda.stream(s_in):
+            d_in.copy_(host_in, non_blocking=True)
+            d_in2.copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            host_out.copy_(d_out, non_blocking=True)
+
+    both()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        both()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / reps
+    h2d = 2 * host_in.numel() * host_in.element_size()
+    d2h = host_out.numel() * host_out.element_size()
+    return {"seconds_per_step": dt, "h2d_gbs": h2d / dt / 1e9, "d2h_gbs": d2h / dt / 1e9}
+
+
 def cpu_sample(oracle, rows, a_rows=None, b=None):
     """Time the CPU oracle GEMM on `rows` rows of A against the full B; returns (TFLOP/s, seconds)."""
     if b is None:
@@ -407,6 +461,8 @@ def main():
 
     # ---- end to end through the host-buffer C-ABI entry: pinned host operands in, C back out, every step
     e2e_steps = max(3, min(args.steps, 10))
+    all_cores = os.sched_getaffinity(0)
+    numa = pin_to_gpu_numa_node(torch, dev)  # before the pinned buffers exist: their pages land on this node
     ha = a.cpu().pin_memory()
     hb = b.cpu().pin_memory()
     hc = torch.empty((M_PER_RANK, N_DIM), dtype=torch.float32).pin_memory()
@@ -422,6 +478,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = FLOPS_PER_STEP * world / float(t.item()) / 1e12
     e2e_ok = bool(torch.equal(hc.to(dev), c))
+    # The ceiling the host link puts on that number: plain pinned copies of one step's bytes, host to device
+    # and device to host at the same time, on every rank at once (one cudaMemcpyAsync per direction).
+    link = host_link_ceiling(torch, dev, ha, hc, barrier)
+    lt = torch.tensor([link["seconds_per_step"]], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    link_ceiling_tflops = FLOPS_PER_STEP * world / float(lt.item()) / 1e12
+    os.sched_setaffinity(0, all_cores)  # the CPU-baseline leg below uses every core again
 
     # ---- context: the vendor library on the same operands, same protocol (not the product path)
     # fp16 in / fp32 out is the like-for-like figure (the call of gemm/gemm_test.cu:249-261 with fp16 operands);
@@ -499,7 +563,12 @@ def main():
             "vs_baseline": None, "dtype": "f16 in, f32 accumulate", "data": "synthetic", "config": config_dict(world),
             "clocks": dict(clocks.summary(), sm_mhz_in_kernel=in_kernel_mhz),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM,
-                    "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
+                    "d2h_bytes_per_step": 4 * M_PER_RANK * N_DIM, "steps": e2e_steps, "result_matches_device_run": e2e_ok,
+                    "link_ceiling_gbs": {"h2d": link["h2d_gbs"], "d2h": link["d2h_gbs"],
+                                         "how": "rank 0's pinned copies of one step's bytes, both directions at once, "
+                                                "while every rank does the same"},
+                    "link_ceiling_tflops": link_ceiling_tflops, "frac_of_link": e2e_value / link_ceiling_tflops,
+                    "host_numa": numa},
             "gpu_launches": args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline, "sustained": sustained,
             "other_configs": other,
             "context": {"cublas_tflops_same_protocol": cublas_tflops,

@@ -31,7 +31,10 @@ enum class gemm_sm100_k_mode
 {
     output_stationary,
     split_k_outer,
-    stream_k,  // the last partial wave of tiles is cut along K over all CTA pairs (gemm_sm90_k_mode::stream_k_*)
+    split_k_inner,  // the K ranges of a tile are neighbours in the schedule (gemm_sm90_k_mode::split_k_inner)
+    stream_k,  // the last partial wave of tiles is cut along K over all CTA pairs (the schedule of both
+               // gemm_sm90_k_mode::stream_k_* flavours, which differ in code structure only).  Kept for
+               // parity of the mode list; `automatic` is the mode to use: it is faster on every shape measured.
     automatic, // output_stationary, or split_k_outer with a split count chosen to fill the waves (few tiles, long K)
 };
 
@@ -58,10 +61,13 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
         t = swapped;
     }
     int rc;
-    if ((k_mode == gemm_sm100_k_mode::split_k_outer && split_k > 1) || k_mode == gemm_sm100_k_mode::stream_k ||
-        k_mode == gemm_sm100_k_mode::automatic) {
+    const bool is_split = (k_mode == gemm_sm100_k_mode::split_k_outer || k_mode == gemm_sm100_k_mode::split_k_inner) && split_k > 1;
+    if (is_split || k_mode == gemm_sm100_k_mode::stream_k || k_mode == gemm_sm100_k_mode::automatic) {
         const int block_n = variant ? variant : (t.N <= 64 ? 64 : (t.N <= 128 ? 128 : 256));
-        const int split = k_mode == gemm_sm100_k_mode::stream_k ? -1 : (k_mode == gemm_sm100_k_mode::automatic ? 0 : split_k);
+        const int split = k_mode == gemm_sm100_k_mode::stream_k     ? -1
+                          : k_mode == gemm_sm100_k_mode::automatic   ? 0
+                          : k_mode == gemm_sm100_k_mode::split_k_inner ? -split_k
+                                                                        : split_k;
         rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, 2, split, 0, stream);
     } else {
         rc = spork_gemm_sm100_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, variant, stream);

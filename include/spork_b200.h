@@ -34,6 +34,7 @@ extern "C" {
 #define SPORK_ERR_DRIVER 10004         /* tensor-map encode or driver entry point failed */
 #define SPORK_ERR_DEVICE_TIMEOUT 10005 /* a bounded device-side wait ran out (status word set) */
 #define SPORK_ERR_TOO_LARGE 10006      /* beyond a stated fixed capacity */
+#define SPORK_ERR_DEVICE_CHECK 10007   /* debug build (-DSPORK_CHECKED): a device-side range check failed (status word set) */
 
 /* ---- GEMM: C[M,N] (fp32, row-major) = A[M,K] (fp16, row-major) . B[N,K]^T (fp16, row-major) ----
  * Operand layout of the reference harness's hot call
@@ -47,9 +48,10 @@ extern "C" {
 int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K);
 
 /* Launch.  variant: 0 = choose (width from N, CTA pairs; single CTAs with
- * tiles at most 128 wide for small latency-bound problems), 64 / 128 / 256 =
+ * tiles at most 128 wide for small latency-bound problems; 256 x 512 tiles per
+ * CTA pair for large problems with K >= 4096), 64 / 128 / 256 / 512 =
  * width of the output tile along N, taken literally, on CTA pairs (the
- * n64/n128/n256 variants of xgemm_Sm90_n{64,128,256}.py).
+ * n64/n128/n256 variants of xgemm_Sm90_n{64,128,256}.py; 512 has no counterpart).
  * Replaces matmul_sm90(t, gemm_sm90_k_mode::output_stationary, stream)
  * (gemm/gemm_sm90.cu:1344-1360). */
 int spork_gemm_sm100_f16f32(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int variant,
@@ -79,7 +81,16 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
  *             (gemm/gemm_sm90.h:10-11, gemm/gemm_sm90.cu:1004-1094): whole
  *             waves of tiles run one tile per CTA pair, the K blocks of the
  *             last partial wave are dealt out evenly over all CTA pairs and
- *             reduce-added into their (zeroed) tiles
+ *             reduce-added into their (zeroed) tiles.  A compatibility mode:
+ *             CTA pairs that share a tile sit at different K offsets, so
+ *             concurrent tiles no longer sweep shared strips of A and B through
+ *             L2 together, and split_k = 0 is faster on every shape measured.
+ *             <= -2: |split_k| ranges like >= 2, but the ranges of one tile are
+ *             neighbours in the schedule (K fastest), the counterpart of
+ *             gemm_sm90_k_mode::split_k_inner (gemm/gemm_sm90.h:9).
+ *   block_n   also 512: 256 x 512 tiles per CTA pair (cta_group 2, split_k >= 0
+ *             or <= -2), the tile the library picks by itself for large
+ *             compute-bound problems with K >= 4096.
  *   max_ctas  0 = one CTA per SM, else an upper bound on the grid. */
 int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                int block_n, int cta_group, int split_k, int max_ctas, void* stream);
@@ -167,6 +178,13 @@ int spork_gemm_sm100_ring_model(uint32_t M, uint32_t N, uint32_t K, int block_n,
                                 int max_ctas, int sm_count, int stages, int skew, uint32_t seed, uint32_t group,
                                 int inject, uint64_t* stats);
 
+/* Every GEMM launch needs three TMA descriptors (tensor maps).  They are encoded
+ * by the driver once per (base address, shape, tile box, element type) and host
+ * thread and reused by later launches on the same operands; this returns how many
+ * look-ups of the process hit and missed that cache.  The reference encodes them
+ * on every launch (gemm/gemm_sm90.cu:1167-1206). */
+int spork_gemm_sm100_tmap_cache_stats(uint64_t* hits, uint64_t* misses);
+
 /* Tracing of the 256 x 512 kernel: later launches make their first CTA write SM
  * clock stamps (clock64) of its tile hand-overs into `device_buffer`, eight
  * 64-bit values per work item of that CTA, for the first `items` work items:
@@ -215,6 +233,18 @@ int spork_gemm_sm100_status(void* stream, uint32_t* detail);
  * reports SPORK_ERR_DEVICE_TIMEOUT and the context stays usable.  The reference
  * spins without bound (gemm/gemm_sm90.cu:434-440) and has no such path. */
 int spork_selftest_bounded_wait(uint32_t limit_us, void* stream);
+
+/* Self-test of the debug build's range checks (libspork_b200_checked.so, built with
+ * -DSPORK_CHECKED: the kernels test every shared-memory and tensor-memory address
+ * and every TMA coordinate against what they allocated, record the first failure
+ * in the status word and skip the access).  which = 0 / 1 / 2 asks the checks
+ * about a shared-memory range, a tensor-memory column range or a TMA coordinate
+ * that is out of bounds - nothing is accessed - so that the next
+ * spork_gemm_sm100_status reports SPORK_ERR_DEVICE_CHECK with detail
+ * 0xC0000000 | (0x701 + which) << 16; which = 3 asks three legal questions and
+ * leaves the word clear.  In the normal build: SPORK_ERR_UNSUPPORTED_SHAPE.  The
+ * reference's counterpart is DEVICE_ASSERT (gemm/gemm_sm90.cu:15), a trap. */
+int spork_selftest_range_check(int which, void* stream);
 
 /* Host-buffer convenience (the htod_f32_* pattern of tk_4090_fwd.hpp:7): copies
  * A and B to the device, runs the GEMM, copies C back and synchronises.  A and B

@@ -30,6 +30,7 @@ from .api import (  # noqa: F401
     matmul_sm100_tf32,
     status,
     ring_model,
+    tmap_cache_stats,
     trace,
     tune,
     tuning,

@@ -14,7 +14,9 @@ import os
 import struct
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libspork_b200.so")
+# SPORK_B200_LIBRARY selects another build of the library (the range-checked debug build
+# libspork_b200_checked.so of `python -m spork_b200.build --checked`).
+_LIB_PATH = os.environ.get("SPORK_B200_LIBRARY") or os.path.join(_HERE, "libspork_b200.so")
 
 # Fixture codes of init_test_data: 0..2 are the reference's TestDataCode (gemm/gemm_test.h:6-11).
 DATA_RANDOM, DATA_IDENTITY, DATA_TILED_NUMBERS, DATA_UNIFORM_PM1, DATA_NORMAL = range(5)
@@ -30,6 +32,7 @@ _ERR_NAMES = {
     10004: "driver call failed (tensor map encode)",
     10005: "a bounded device-side wait ran out",
     10006: "size beyond the fixed capacity of this entry point",
+    10007: "a range check of the debug build failed on the device",
 }
 
 
@@ -71,6 +74,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_f16f32_static.restype = i32
         L.spork_selftest_bounded_wait.argtypes = [u32, vp]
         L.spork_selftest_bounded_wait.restype = i32
+        L.spork_selftest_range_check.argtypes = [i32, vp]
+        L.spork_selftest_range_check.restype = i32
         L.spork_gemm_sm100_last_clock_mhz.argtypes = [vp, ctypes.POINTER(ctypes.c_double)]
         L.spork_gemm_sm100_last_clock_mhz.restype = i32
         L.spork_gemm_sm100_tune.argtypes = [i32, i32, i32, i32]
@@ -78,6 +83,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_ring_model.argtypes = [u32, u32, u32, i32, i32, i32, i32, i32, i32, i32, u32, u32, i32,
                                                   ctypes.POINTER(ctypes.c_uint64)]
         L.spork_gemm_sm100_ring_model.restype = i32
+        L.spork_gemm_sm100_tmap_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
+        L.spork_gemm_sm100_tmap_cache_stats.restype = i32
         L.spork_gemm_sm100_trace.argtypes = [vp, u32]
         L.spork_gemm_sm100_trace.restype = i32
         L.spork_gemm_sm100_tuning.argtypes = [ctypes.POINTER(i32), i32]
@@ -258,6 +265,13 @@ def ring_model(M: int, N: int, K: int, *, block_n: int = 256, cta_group: int = 2
     rc = lib().spork_gemm_sm100_ring_model(M, N, K, block_n, cta_group, split_k, max_ctas, sm_count, stages, skew, seed,
                                            group, inject, stats)
     return rc, {"items": int(stats[0]), "mma_ops": int(stats[1]), "steps": int(stats[2]), "groups": int(stats[3])}
+
+
+def tmap_cache_stats() -> tuple[int, int]:
+    """(hits, misses) of the per-thread cache of encoded TMA descriptors, summed over the process."""
+    h, m = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    _check(lib().spork_gemm_sm100_tmap_cache_stats(ctypes.byref(h), ctypes.byref(m)), "spork_gemm_sm100_tmap_cache_stats")
+    return int(h.value), int(m.value)
 
 
 def trace(buffer=None) -> None:

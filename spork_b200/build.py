@@ -29,11 +29,20 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile each .cu to an object (only when stale) and link the shared library."""
+CHECKED_LIB = os.path.join(HERE, "libspork_b200_checked.so")
+
+
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
+    """Compile each source to an object (only when stale) and link the shared library.
+
+    ``checked=True`` builds the debug variant ``libspork_b200_checked.so`` (-DSPORK_CHECKED: the kernels
+    range-check every shared-memory and tensor-memory address and every TMA coordinate and report through
+    the device status word); select it at run time with the environment variable SPORK_B200_LIBRARY."""
     headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
         glob.glob(os.path.join(HERE, "..", "include", "*.h"))
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_checked" if checked else "build")
+    lib = CHECKED_LIB if checked else LIB
+    flags = FLAGS + (["-DSPORK_CHECKED"] if checked else [])
     os.makedirs(objdir, exist_ok=True)
     objs = []
     procs = []
@@ -41,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(objdir, os.path.splitext(os.path.basename(src))[0] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = [NVCC] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, p in procs:
         out, _ = p.communicate()
@@ -49,10 +58,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         if p.returncode:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    if force or procs or _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs
+    if force or procs or _stale(lib, objs):
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib] + objs
         subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 def build_harness() -> str:
@@ -69,6 +78,6 @@ def build_harness() -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv))
     if "--harness" in sys.argv:
         print(build_harness())

@@ -14,7 +14,10 @@
 //   warp  9    tcgen05.mma issuer (the whole warp runs the control flow, an elected lane issues) and TMEM owner
 //   warps 10-11 idle: they complete the third warpgroup, so that whole warpgroups can trade
 //              registers (setmaxnreg): 216 per softmax thread, 72 for the rest
-// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
+// Tensor memory (512 columns): score buffers of 128 fp32 columns, then O0 | O1 of D columns each.  Head
+// dimension 128: two score buffers, one per query tile.  Head dimension 64: three, used in rotation by the
+// (tile, block) pairs in issue order, so the next score tile of a query tile is ready before its softmax
+// has finished the current one (see Config::kScoreBufs).
 // Per key block j and query tile w:
 //   S_w = Q_w K_j^T            tcgen05.mma, both operands K-major in shared memory
 //   softmax thread: reads its whole S row into registers, row max,
@@ -29,7 +32,8 @@
 //       fp16 range)
 //   O_w += P_w V_j             tcgen05.mma, A = P_w from tensor memory, B = V_j (N-major)
 // The two query tiles alternate, so the tensor core works on one tile while the
-// other tile's softmax runs.  Keys past the end of a ragged sequence are masked
+// other tile's softmax runs.  With a causal mask each tile stops at its own diagonal block.
+// Keys past the end of a ragged sequence are masked
 // to -inf; rows past the end are computed on zero-filled queries and not stored.
 // Every wait on a barrier is bounded (see ptx_sm100.cuh); the one wait that is not, setmaxnreg's for free
 // registers, cannot block because the trade fits the launch allocation (static_assert below).
@@ -77,6 +81,14 @@ struct Config {
     static constexpr int kKvStages = kStagesFit > kMaxKvStages ? kMaxKvStages : kStagesFit;
     static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + kKvStages * kTileBytes + 1024;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory limit");
+    // Score buffers in tensor memory, 128 fp32 columns each, used in rotation by the (query tile, key block)
+    // pairs in issue order.  With head dimension 128 the two O accumulators take half of tensor memory and two
+    // buffers remain: one per query tile, and S_w(j+1) can only be issued once P_w(j) V_j has consumed the
+    // buffer.  With head dimension 64 the accumulators take 128 columns and a third buffer fits: the next
+    // score tile is computed while the previous one is still being exponentiated, so a query tile's softmax
+    // goes from block to block without waiting for the tensor core.
+    static constexpr int kScoreBufs = D == 64 ? 3 : 2;
+    static_assert(kScoreBufs * 128 + 2 * D <= kTmemCols, "tensor memory budget");
 };
 
 struct Params {
@@ -93,9 +105,9 @@ struct Barriers {
     uint64_t q_full;
     uint64_t kv_full[kMaxKvStages];
     uint64_t kv_empty[kMaxKvStages];
-    uint64_t s_full[2];
-    uint64_t p_ready[2][2];  // [query tile][key half]
-    uint64_t pv_done[2];
+    uint64_t s_full[3];      // per score buffer
+    uint64_t p_ready[3][2];  // [score buffer][key half]
+    uint64_t pv_done[2];     // per query tile
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -227,10 +239,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // causal: the pairs with the most key blocks are launched first, so the short ones fill the tail
     const int q_pair = p.causal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
     const int q_row0 = q_pair * 2 * kTileQ;
-    // causal: keys beyond this CTA's last query row are never needed (both tiles walk the same blocks; the
-    // first tile sees its last block fully masked)
-    const int last_row = q_row0 + 2 * kTileQ - 1 < p.S - 1 ? q_row0 + 2 * kTileQ - 1 : p.S - 1;
-    const int n_blocks = p.causal ? last_row / kTileKV + 1 : p.kv_blocks;
+    // Key blocks each query tile walks.  Causal: keys beyond a tile's last query row are never needed, so
+    // the first tile stops one block before the second (it used to walk a fully masked block).
+    const int last_row0 = q_row0 + kTileQ - 1 < p.S - 1 ? q_row0 + kTileQ - 1 : p.S - 1;
+    const int last_row1 = q_row0 + 2 * kTileQ - 1 < p.S - 1 ? q_row0 + 2 * kTileQ - 1 : p.S - 1;
+    const int n_blocks0 = p.causal ? last_row0 / kTileKV + 1 : p.kv_blocks;
+    const int n_blocks = p.causal ? last_row1 / kTileKV + 1 : p.kv_blocks;   // second tile; n_blocks >= n_blocks0
+    // The (query tile, key block) pairs in issue order, "uses" u = 0, 1, ...: (0,0), (1,0), (0,1), (1,1), ...
+    // and, when the first tile has one block fewer, (1, n_blocks - 1) last.  Use u works in score buffer
+    // u % kScoreBufs, on barrier phase (u / kScoreBufs) & 1 of that buffer's barriers.
+    constexpr int kBufs = Cfg::kScoreBufs;
+    const int n_uses = n_blocks0 + n_blocks;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
@@ -238,11 +257,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             mbar_init(smem_u32(&bars->kv_full[s]), 1);
             mbar_init(smem_u32(&bars->kv_empty[s]), 1);
         }
-        for (int w = 0; w < 2; ++w) {
-            mbar_init(smem_u32(&bars->s_full[w]), 1);
+        for (int b = 0; b < 3; ++b) {
+            mbar_init(smem_u32(&bars->s_full[b]), 1);
             for (int h = 0; h < 2; ++h) {
-                mbar_init(smem_u32(&bars->p_ready[w][h]), kTileQ);
+                mbar_init(smem_u32(&bars->p_ready[b][h]), kTileQ);
             }
+        }
+        for (int w = 0; w < 2; ++w) {
             mbar_init(smem_u32(&bars->pv_done[w]), 1);
         }
         bars->abort_flag = 0;
@@ -262,8 +283,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     // column offsets inside the allocation
-    const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128; P_w (fp16 pairs) reuses its first 64 columns
-    const uint32_t tmem_o0 = tmem_base + 256;    // O_w at + w * 128
+    const uint32_t tmem_s0 = tmem_base;                // score buffer b at + b * 128; P (16-bit pairs) reuses its first 64 columns
+    const uint32_t tmem_o0 = tmem_base + kBufs * 128;  // O_w at + w * D
 
     // The softmax keeps a whole row of 128 scores in registers and needs room beside them to overlap
     // the exponentials' latencies; the loader and the issuer need almost none. Whole warpgroups trade.
@@ -282,7 +303,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int t = 0; t < 2 * n_blocks && ok; ++t) {
+            for (int t = 0; t < 2 * n_blocks && ok; ++t) {  // the second tile's blocks cover the first's
                 // tile order: K_0, V_0, K_1, V_1, ...
                 const int j = t >> 1;
                 const CUtensorMap* map = (t & 1) ? &tmap_v : &tmap_k;
@@ -312,46 +333,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const bool leader = elect_one();
         constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false, kBf16);
         constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true, kBf16);  // B = V is N-major
-        uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
         bool ok = true;
-        auto advance = [&]() {
-            if (++stage == (uint32_t)kKvStages) {
-                stage = 0;
-                phase ^= 1u;
-            }
-        };
         // Descriptor low words: one per operand tile, advanced by compile-time constants per MMA
         // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
         // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
         const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
-        // S_w = Q_w K^T from the K tile in ring slot `st`. (Not split along the keys: with both operands
-        // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
-        auto issue_qk = [&](int w, uint32_t st) {
-            const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
-            const uint32_t q_lo = q_lo0 + (uint32_t)w * (Cfg::kTileBytes >> 4);
-            if (leader) {
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)((kk / 4) * (Cfg::kAtomBytes >> 4) + 2 * (kk % 4));
-                    umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
-                                     kk != 0 ? 1u : 0u);
-                }
-                umma_commit<1>(smem_u32(&bars->s_full[w]));
-            }
-        };
-        // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
-        // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart);
-        // half h covers keys [64 h, 64 h + 64)
-        auto issue_pv = [&](int w, uint32_t st, bool accumulate, int h) {
-            const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
-            if (leader) {
-#pragma unroll
-                for (int kk = h * (kTileKV / 32); kk < (h + 1) * (kTileKV / 32); ++kk) {
-                    umma_f16_ts_cta1(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
-                                     kDescHiSw128, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
-                }
-            }
-        };
         auto commit = [&](uint64_t* bar) {
             if (leader) {
                 umma_commit<1>(smem_u32(bar));
@@ -365,62 +351,98 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             return __all_sync(0xFFFFFFFFu, done);
         };
+        // use u -> (key block j, query tile w); K_j is tile 2j of the ring, V_j tile 2j + 1
+        auto use_block = [&](int u, int& j, int& w) {
+            if (u < 2 * n_blocks0) {
+                j = u >> 1;
+                w = u & 1;
+            } else {
+                j = n_blocks - 1;
+                w = 1;
+            }
+        };
+        auto wait_kv = [&](int t, uint32_t& st) {
+            st = (uint32_t)(t % kKvStages);
+            return wait(&bars->kv_full[st], (uint32_t)((t / kKvStages) & 1), st);
+        };
+        // S(u) = Q_w K_j^T into score buffer u % kBufs.  (Not split along the keys: with both operands
+        // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
+        auto issue_qk = [&](int u) {
+            int j, w;
+            use_block(u, j, w);
+            uint32_t st;
+            if (!wait_kv(2 * j, st)) {
+                return false;
+            }
+            tcgen05_fence_after();
+            const uint32_t buf = (uint32_t)(u % kBufs);
+            const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
+            const uint32_t q_lo = q_lo0 + (uint32_t)w * (Cfg::kTileBytes >> 4);
+            if (leader) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)((kk / 4) * (Cfg::kAtomBytes >> 4) + 2 * (kk % 4));
+                    umma_f16_ss_cta1(tmem_s0 + buf * 128, q_lo + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
+                                     kk != 0 ? 1u : 0u);
+                }
+                umma_commit<1>(smem_u32(&bars->s_full[buf]));
+                if (w == 1) {
+                    umma_commit<1>(smem_u32(&bars->kv_empty[st]));  // the second tile is K_j's last reader
+                }
+            }
+            return true;
+        };
+        // O_w (+)= P(u) V_j: A = P in tensor memory (16 keys = 8 packed columns per step), B = the V tile
+        // (N-major; its d-halves are one 128-row block apart), in two halves of 64 keys as the softmax
+        // hands them over
+        auto issue_pv = [&](int u) {
+            int j, w;
+            use_block(u, j, w);
+            uint32_t st;
+            // the tile was requested long ago; make sure of it now, while the softmax is still at work
+            if (!wait_kv(2 * j + 1, st)) {
+                return false;
+            }
+            const uint32_t buf = (uint32_t)(u % kBufs), parity = (uint32_t)((u / kBufs) & 1);
+            const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (!wait(&bars->p_ready[buf][h], parity, 0x30 + 8 * h + buf)) {
+                    return false;
+                }
+                tcgen05_fence_after();
+                if (leader) {
+#pragma unroll
+                    for (int kk = h * (kTileKV / 32); kk < (h + 1) * (kTileKV / 32); ++kk) {
+                        umma_f16_ts_cta1(tmem_o0 + w * D, tmem_s0 + buf * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
+                                         kDescHiSw128, idesc_pv, (j > 0 || kk != 0) ? 1u : 0u);
+                    }
+                }
+            }
+            // With three score buffers the softmax of the next block may already be running and may want to
+            // rescale O_w: it waits for this.  With two, only the end of the tile matters (a completed
+            // s_full of the next block implies this multiply is complete).
+            const int n_w = w == 0 ? n_blocks0 : n_blocks;
+            if (kBufs == 3 || j == n_w - 1) {
+                commit(&bars->pv_done[w]);
+            }
+            if (w == 1) {
+                commit(&bars->kv_empty[st]);  // the second tile is V_j's last reader
+            }
+            return true;
+        };
         do {
             if (!wait(&bars->q_full, 0, 0x20)) {
                 break;
             }
-            // prologue: S_0(0), S_1(0)
-            if (!wait(&bars->kv_full[stage], phase, stage)) {
-                break;
+            for (int u = 0; u < kBufs && u < n_uses && ok; ++u) {
+                ok = issue_qk(u);
             }
-            tcgen05_fence_after();
-            issue_qk(0, stage);
-            issue_qk(1, stage);
-            commit(&bars->kv_empty[stage]);
-            advance();
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                const uint32_t v_stage = stage, v_phase = phase;
-                advance();
-                const uint32_t k_stage = stage, k_phase = phase;  // K_{j+1}, if any
-                const bool more = j + 1 < n_blocks;
-                if (more) {
-                    advance();
-                }
-                // The tiles this block's multiplies read were requested long ago; make sure of them now, while
-                // the softmax is still at work, so that nothing stands between P arriving and the issue.
-                if (!wait(&bars->kv_full[v_stage], v_phase, v_stage) ||
-                    (more && !wait(&bars->kv_full[k_stage], k_phase, k_stage))) {
-                    ok = false;
-                    break;
-                }
-#pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    if (!ok) {
-                        break;
-                    }
-                    if (!wait(&bars->p_ready[w][0], (uint32_t)(j & 1), 0x30 + w)) {
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    issue_pv(w, v_stage, j > 0, 0);  // the first 64 keys, while the softmax does the rest
-                    if (!wait(&bars->p_ready[w][1], (uint32_t)(j & 1), 0x38 + w)) {
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    issue_pv(w, v_stage, true, 1);
-                    if (more) {
-                        issue_qk(w, k_stage);
-                    } else {
-                        commit(&bars->pv_done[w]);  // completes once: O_w is final
-                    }
-                    if (w == 1) {
-                        commit(&bars->kv_empty[v_stage]);
-                        if (more) {
-                            commit(&bars->kv_empty[k_stage]);
-                        }
-                    }
+            // P(u) V, then the score tile that takes over the buffer this multiply frees
+            for (int u = 0; u < n_uses && ok; ++u) {
+                ok = issue_pv(u);
+                if (ok && u + kBufs < n_uses) {
+                    ok = issue_qk(u + kBufs);
                 }
             }
         } while (false);
@@ -432,22 +454,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t quarter = warp % 4;  // TMEM lanes [32*quarter, +32)
         const uint32_t row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32u) << 16;
-        const uint32_t tmem_s = tmem_s0 + w * 128 + lane_addr;
-        const uint32_t tmem_o = tmem_o0 + w * 128 + lane_addr;
+        const uint32_t tmem_o = tmem_o0 + w * D + lane_addr;
         const float sl2 = p.scale_log2e;
         float m_ref = -INFINITY;  // row max the stored O and l are relative to (raw scores)
         float l_run = 0.0f;       // running row sum
         bool ok = true;
-        for (int j = 0; j < n_blocks; ++j) {
-            if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, kSoftmaxBackoffNs)) {
+        const int n_w = w == 0 ? n_blocks0 : n_blocks;  // key blocks of this query tile
+        for (int j = 0; j < n_w; ++j) {
+            // this (tile, block) pair's place in the issue order, hence its score buffer and barrier phase
+            const int u = w == 0 ? 2 * j : 2 * j + (j < n_blocks0 ? 1 : 0);
+            const uint32_t buf = (uint32_t)(u % kBufs), parity = (uint32_t)((u / kBufs) & 1);
+            const uint32_t tmem_s = tmem_s0 + buf * 128 + lane_addr;
+            if (!mbar_wait(smem_u32(&bars->s_full[buf]), parity, abort_flag, kSoftmaxBackoffNs)) {
                 if (lane == 0) {
-                    report_timeout(p, abort_flag, 3, 0x10 + w);
+                    report_timeout(p, abort_flag, 3, 0x10 + buf);
                 }
                 ok = false;
                 break;
             }
-            // A completed s_full also means every earlier MMA of the issuing thread is complete: P_w of the
-            // previous block has been consumed and O_w is not being written.
+            // With two score buffers a completed s_full also means every earlier MMA of the issuing thread is
+            // complete: P_w of the previous block has been consumed and O_w is not being written.  With three
+            // the previous block's P V may still be running; whoever rescales O_w waits for it below.
             tcgen05_fence_after();
             uint32_t r[128];
             {
@@ -502,6 +529,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             // It has to be finished before the first half of P is handed over: from then on the issuer
             // accumulates into O_w.
             if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
+                if (kBufs == 3) {
+                    // O_w must have taken the previous block's P V before it is rescaled.  That multiply is the
+                    // j-th completion of pv_done[w] (this block's cannot be issued before this thread hands P
+                    // over), so the barrier has completed j - 1 or j phases: wait for parity (j - 1) & 1.
+                    if (!mbar_wait(smem_u32(&bars->pv_done[w]), (uint32_t)((j - 1) & 1), abort_flag)) {
+                        if (lane == 0) {
+                            report_timeout(p, abort_flag, 3, 0x18 + w);
+                        }
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                }
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
@@ -544,7 +584,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 // hand this half of P_w over: the issuer multiplies it while the other half is computed
                 tmem_st_wait();
                 tcgen05_fence_before();
-                mbar_arrive(smem_u32(&bars->p_ready[w][half]));
+                mbar_arrive(smem_u32(&bars->p_ready[buf][half]));
             }
             float l_blk0, l_blk1;
             unpack2(l_blk2, l_blk0, l_blk1);
@@ -552,7 +592,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         // ---- epilogue: O_w / l -> fp16 -> global
         if (ok) {
-            if (!mbar_wait(smem_u32(&bars->pv_done[w]), 0u, abort_flag, 20)) {
+            // two score buffers: pv_done[w] completes once, at the end; three: once per block
+            if (!mbar_wait(smem_u32(&bars->pv_done[w]), kBufs == 3 ? (uint32_t)((n_w - 1) & 1) : 0u, abort_flag, 20)) {
                 if (lane == 0) {
                     report_timeout(p, abort_flag, 3, 0x28 + w);
                 }

@@ -121,7 +121,8 @@ extern "C" int spork_gemm_sm100_status(void* stream, uint32_t* detail)
     if (word != 0) {
         cudaMemsetAsync(dev->status_word, 0, sizeof(word), s);
         cudaStreamSynchronize(s);
-        return SPORK_ERR_DEVICE_TIMEOUT;
+        // 0xC.......: a range check of the debug build; anything else: a bounded wait that ran out
+        return (word >> 28) == 0xCu ? SPORK_ERR_DEVICE_CHECK : SPORK_ERR_DEVICE_TIMEOUT;
     }
     return 0;
 }

@@ -19,6 +19,7 @@ struct Params {
     uint32_t M, N, K;
     uint32_t tiles_m, tiles_n;   // output tiles (tile = kBlockM*CG x BLOCK_N)
     uint32_t split_k;            // >= 1
+    uint32_t split_inner;        // 1: the K ranges of one tile are neighbours in the work list (K fastest), 0: K slowest
     uint32_t batches;            // >= 1: independent problems A[l] * B[l]^T -> C[l], contiguous in memory
     uint32_t kb_per_split;       // K blocks per split
     uint32_t num_kb;             // ceil(K / kBlockK)
@@ -91,10 +92,14 @@ SPORK_HD WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i
     if (p.sk_tiles == 0) {
         const uint32_t item = g + i * G;
         const uint32_t tiles = p.tiles_m * p.tiles_n;
-        const uint32_t q = item / tiles;   // (batch, split), split fastest
-        w.batch = q / p.split_k;
-        w.split = q % p.split_k;
-        decode_tile(p, item % tiles, w);
+        // Within a batch entry the list is either tile-fastest (every tile's first K range, then every
+        // tile's second one: gemm_sm90_k_mode::split_k_outer) or K-fastest (a tile's ranges are neighbours,
+        // so they run at the same time on different CTA groups: split_k_inner), gemm/gemm_sm90.cu:1096-1114.
+        const uint32_t per_batch = tiles * p.split_k;
+        const uint32_t r = item % per_batch;
+        w.batch = item / per_batch;
+        w.split = p.split_inner ? r % p.split_k : r / tiles;
+        decode_tile(p, p.split_inner ? r / p.split_k : r % tiles, w);
         w.kb_begin = w.split * p.kb_per_split;
         const uint32_t e = w.kb_begin + p.kb_per_split;
         w.kb_end = e < p.num_kb ? e : p.num_kb;

@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 #include <stdint.h>
 #include <stdio.h>
@@ -162,6 +163,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
+    // Debug builds test every address and coordinate below against these ranges (see Checker).
+    const Checker chk{p.status, smem_base, smem_u32(smem_raw) + (uint32_t)Cfg::kSmemBytes, tmem_base,
+                      (uint32_t)Cfg::kTmemCols};
+    constexpr uint32_t kOperandBytes = kTf32 ? 4u : 2u;
+
     // Everything above is independent of earlier work in the stream.  When launched as a programmatic
     // dependent, this CTA may have been set up while the previous kernel was still running on other SMs;
     // from here on it reads and writes global memory, so the previous kernel must be complete.  The next
@@ -197,6 +203,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
                     const uint32_t sb = sa + Cfg::kABytes;
                     const uint32_t full = smem_u32(&bars->full[stage]);
+                    const bool loads_ok =
+                        chk.smem(sa, Cfg::kStageBytes, 1024u, 0x11) &&
+                        chk.tma_coords((int32_t)(kb * KATOMS * kElemsK), kOperandBytes, a_row, (int32_t)w.batch, 0x12) &&
+                        chk.tma_coords((int32_t)((kb * KATOMS + KATOMS - 1) * kElemsK), kOperandBytes, b_row, 0, 0x13);
+                    if (!loads_ok) {
+                        ok = false;   // recorded; the other roles end through their bounded waits
+                        *abort_flag = 1u;
+                        break;
+                    }
                     if ((p.experiment & 2u) && issued >= p.stages) {
                         if (is_leader) {
                             mbar_arrive(full);  // hand the stale stage over without loading
@@ -280,6 +295,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                     tcgen05_fence_after();
                     const uint32_t sa = ring_base + stage * Cfg::kStageBytes;
+                    if (!(chk.smem(sa, Cfg::kStageBytes, 1024u, 0x21) && chk.tmem(tmem_d, Cfg::kAccCols, 0x22))) {
+                        *abort_flag = 1u;
+                        ok = false;
+                        break;
+                    }
                     if (elected) {
 #pragma unroll
                         for (int at = 0; at < KATOMS; ++at) {
@@ -348,6 +368,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll 1
             for (int c = 0; c < BLOCK_N / kEpiCols; ++c) {
                 uint32_t r[32];
+                if (!chk.tmem(taddr0 + c * kEpiCols, kEpiCols, 0x31)) {
+                    continue;
+                }
                 tmem_ld_32x32b_x32(taddr0 + c * kEpiCols, r);
                 tmem_ld_wait();
                 const uint32_t col = col0 + c * kEpiCols;
@@ -370,6 +393,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (kWorkspace || p.use_tma_store) {
                     const uint32_t slab = slab0 + slab_sel * kSlabBytes;
                     slab_sel ^= 1u;
+                    if (!(chk.smem(slab, kSlabBytes, 1024u, 0x32) &&
+                          chk.tma_coords((int32_t)col, 4u, (int32_t)row0, (int32_t)(kWorkspace ? w.split : w.batch), 0x33))) {
+                        continue;
+                    }
                     // The store issued two chunks ago read this slab; make sure it is done.
                     if (lane == 0) {
                         bulk_wait_group_read<kSlabsPerWarp - 1>();
@@ -498,10 +525,70 @@ static EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
+// Encoded tensor maps are remembered per host thread, keyed by everything that goes into the encoding
+// (base address, extents, box, element type): a launch on operands seen before costs no driver call
+// (the reference encodes three maps on every launch, gemm/gemm_sm90.cu:1167-1206, about a microsecond
+// each).  A map describes addresses and shapes only, never contents, so an entry cannot go stale: memory
+// freed and allocated again at the same address with the same shape is described by the same map.
+struct TmapKey {
+    const void* base;
+    uint64_t rows, cols, batches;
+    uint32_t box_rows, box_cols, dtype, dims;
+    bool operator==(const TmapKey& o) const
+    {
+        return base == o.base && rows == o.rows && cols == o.cols && batches == o.batches && box_rows == o.box_rows &&
+               box_cols == o.box_cols && dtype == o.dtype && dims == o.dims;
+    }
+};
+
+struct TmapCache {
+    static constexpr int kSlots = 64;  // direct mapped
+    struct Slot {
+        bool valid = false;
+        TmapKey key{};
+        CUtensorMap map;
+    };
+    Slot slots[kSlots];
+    uint64_t hits = 0, misses = 0;
+    static uint32_t slot_of(const TmapKey& k)
+    {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.rows * 0xC2B2AE3D27D4EB4Full) ^ (k.cols * 0x165667B19E3779F9ull) ^ (k.batches << 40) ^
+             ((uint64_t)k.box_rows << 20) ^ ((uint64_t)k.box_cols << 8) ^ k.dtype ^ ((uint64_t)k.dims << 4);
+        return (uint32_t)((h >> 32) % kSlots);
+    }
+};
+static thread_local TmapCache t_tmap_cache;
+static std::atomic<uint64_t> g_tmap_hits{0}, g_tmap_misses{0};
+
+static bool tmap_lookup(const TmapKey& key, CUtensorMap* map)
+{
+    const TmapCache::Slot& s = t_tmap_cache.slots[TmapCache::slot_of(key)];
+    if (s.valid && s.key == key) {
+        *map = s.map;
+        g_tmap_hits.fetch_add(1, std::memory_order_relaxed);
+        return true;
+    }
+    g_tmap_misses.fetch_add(1, std::memory_order_relaxed);
+    return false;
+}
+
+static void tmap_remember(const TmapKey& key, const CUtensorMap& map)
+{
+    TmapCache::Slot& s = t_tmap_cache.slots[TmapCache::slot_of(key)];
+    s.valid = true;
+    s.key = key;
+    s.map = map;
+}
+
 // 2-D row-major tensor map: `cols` is the contiguous dimension.
 static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
                         uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols)
 {
+    const TmapKey key{base, rows, cols, 1, box_rows, box_cols, (uint32_t)dtype, 2};
+    if (tmap_lookup(key, map)) {
+        return 0;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) {
         return SPORK_ERR_DRIVER;
@@ -513,7 +600,11 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     const CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
+    if (r != CUDA_SUCCESS) {
+        return SPORK_ERR_DRIVER;
+    }
+    tmap_remember(key, *map);
+    return 0;
 }
 
 // 3-D map over `batches` such matrices stored one after the other; a box never spans two of them, so
@@ -521,6 +612,10 @@ static int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
 static int make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
                         uint64_t batches, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols)
 {
+    const TmapKey key{base, rows, cols, batches, box_rows, box_cols, (uint32_t)dtype, 3};
+    if (tmap_lookup(key, map)) {
+        return 0;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) {
         return SPORK_ERR_DRIVER;
@@ -532,7 +627,11 @@ static int make_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t el
     const CUresult r = fn(map, dtype, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
+    if (r != CUDA_SUCCESS) {
+        return SPORK_ERR_DRIVER;
+    }
+    tmap_remember(key, *map);
+    return 0;
 }
 
 // Process-wide tuning knobs (spork_gemm_sm100_tune); the defaults are the measured best.
@@ -568,7 +667,8 @@ static uint32_t effective_l2_hints(int tuned)
 
 template <int CG, int BLOCK_N, bool kTf32 = false, int KATOMS = 1>
 static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
-                  int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false, uint32_t batches = 1)
+                  int max_ctas, DeviceState& dev, cudaStream_t stream, bool stream_k = false, uint32_t batches = 1,
+                  bool split_inner = false)
 {
     using Cfg = Config<CG, BLOCK_N, KATOMS>;
     auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS>;
@@ -590,6 +690,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     uint32_t groups = 1;
     plan_launch(p, groups, M, N, K, Cfg::kUmmaM, BLOCK_N, CG, kElemsK * KATOMS, split_k, stream_k, max_ctas,
                 dev.sm_count, batches);
+    p.split_inner = split_inner ? 1u : 0u;
     p.C = C;
     p.status = dev.status_word;
     const Tuning tune = g_tuning;
@@ -658,7 +759,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
 // The 256 x 512 kernel: same plan, maps and status word as launch<2, ...>.
 template <bool kTf32>
 static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, uint32_t split_k,
-                       int max_ctas, DeviceState& dev, cudaStream_t stream)
+                       int max_ctas, DeviceState& dev, cudaStream_t stream, bool split_inner = false)
 {
     using Cfg = WideConfig;
     auto kernel = gemm_wide_kernel<kTf32>;
@@ -679,6 +780,7 @@ static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const 
     Params p{};
     uint32_t groups = 1;
     plan_launch(p, groups, M, N, K, 2 * kBlockM, kWideN, 2, kElemsK, split_k, false, max_ctas, dev.sm_count, 1);
+    p.split_inner = split_inner ? 1u : 0u;
     p.C = C;
     p.status = dev.status_word;
     const Tuning tune = g_tuning;
@@ -686,7 +788,7 @@ static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const 
     p.group_m = tune.wide_group_m >= 1 ? (uint32_t)tune.wide_group_m : (uint32_t)kWideGroupM;
     p.l2_hints = effective_l2_hints(tune.l2_hints);
     p.backoff_ns = (uint32_t)tune.backoff_ns;
-    p.experiment = (uint32_t)tune.experiment & 9u;
+    p.experiment = (uint32_t)tune.experiment & 13u;
     p.wide_skew = tune.wide_skew >= 1 ? (uint32_t)tune.wide_skew : (uint32_t)kWideStages;
     p.trace = tune.trace;
     p.trace_items = tune.trace_items;
@@ -739,7 +841,7 @@ static bool aligned16(const void* p)
 // Whether a problem whose tile is left to the library runs with 256 x 512 tiles.  They move a quarter fewer
 // operand bytes per FLOP, which is what a compute-bound problem at the power limit is short of, but their
 // tiles are twice as coarse: the problem must fill at least two waves of them, waste little of the last
-// tile column, and be deep enough for the skewed tile ends to be a small part of a tile.
+// tile column, and be deep enough for the tile ends to be a small part of a tile.
 static bool want_wide_tiles(uint32_t M, uint32_t N, uint32_t K, int max_ctas, int sm_count)
 {
     if (g_tuning.wide == 1) {
@@ -755,7 +857,10 @@ static bool want_wide_tiles(uint32_t M, uint32_t N, uint32_t K, int max_ctas, in
     const uint64_t tiles_n = (N + kWideN - 1) / kWideN;
     const uint64_t tiles = (uint64_t)((M + 255) / 256) * tiles_n;
     const uint64_t padded_n = tiles_n * kWideN;
-    return groups > 0 && tiles >= 2ull * groups && K >= 1024 && (padded_n - N) * 16 <= N;
+    // K: the tile ends cost about 5000 cycles of tensor-pipe idle time (the epilogue cannot hide behind a
+    // second accumulator), against 1024 cycles per K block; measured at the power limit the wide tile wins
+    // from K = 4096 upwards (8192^3 +6 %, 40016 x 32768 x 6400 +3 %) and loses below (8192 x 8192 x 2048 -6 %).
+    return groups > 0 && tiles >= 2ull * groups && K >= 4096 && (padded_n - N) * 16 <= N;
 }
 
 static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int block_n,
@@ -767,6 +872,11 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     }
     if (M == 0 || N == 0 || batches == 0) {
         return 0;
+    }
+    // split_k <= -2: |split_k| K ranges, K fastest in the work list (gemm_sm90_k_mode::split_k_inner)
+    const bool split_inner = split_k <= -2;
+    if (split_inner) {
+        split_k = -split_k;
     }
     if (batches > 1 && (split_k == -1 || (uint64_t)batches * ((M + 127) / 128) * ((N + 63) / 64) > 0x3FFFFFFFull)) {
         return SPORK_ERR_BAD_ARGUMENT;  // no stream-K over a batch; the item index is 32 bits wide
@@ -795,8 +905,8 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
             return SPORK_ERR_BAD_ARGUMENT;
         }
         const uint32_t sk = split_k == 0 ? 1u : (uint32_t)split_k;
-        return tf32 ? launch_wide<true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream)
-                    : launch_wide<false>(M, N, K, A, B, C, sk, max_ctas, *dev, stream);
+        return tf32 ? launch_wide<true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, split_inner)
+                    : launch_wide<false>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, split_inner);
     }
     if (cta_group == 0) {
         // The caller left the tile to the library.  A problem that fills a small part of one wave and
@@ -831,32 +941,32 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
                                    out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
     if (wide_k && cta_group == 2) {
         switch (block_n) {
-        case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 128: return launch<2, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 256: return launch<2, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
     if (wide_k && cta_group == 1) {
         switch (block_n) {
-        case 64: return launch<1, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 128: return launch<1, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 256: return launch<1, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 64: return launch<1, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 128: return launch<1, 128, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 256: return launch<1, 256, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
 #define SPORK_GEMM_CASE(CG_, BN_)                                                               \
     if (cta_group == CG_ && block_n == BN_) {                                                   \
-        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);        \
+        return launch<CG_, BN_>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);        \
     }
     if (tf32) {
         if (cta_group != 2) {
             return SPORK_ERR_BAD_ARGUMENT;
         }
         switch (block_n) {
-        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
-        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches);
+        case 64: return launch<2, 64, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 128: return launch<2, 128, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+        case 256: return launch<2, 256, true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
         default: return SPORK_ERR_BAD_ARGUMENT;
         }
     }
@@ -1065,7 +1175,10 @@ extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K
             if ((e = cudaGetSymbolAddress(&ptr, g_static_scratch)) != cudaSuccess) {
                 return (int)e;
             }
-            if ((e = cudaMemset(ptr, 0, 256)) != cudaSuccess) {
+            // cleared on the caller's stream and waited for: a blocking memset on the default stream would
+            // not be ordered against a stream created as non-blocking
+            if ((e = cudaMemsetAsync(ptr, 0, 256, stream)) != cudaSuccess ||
+                (e = cudaStreamSynchronize(stream)) != cudaSuccess) {
                 return (int)e;
             }
             d.scratch = static_cast<unsigned char*>(ptr);
@@ -1079,12 +1192,14 @@ extern "C" int spork_gemm_sm100_f16f32_static(uint32_t M, uint32_t N, uint32_t K
             return (int)e;
         }
         uint32_t word = 0;
-        if ((e = cudaMemcpy(&word, dev.scratch, sizeof(word), cudaMemcpyDeviceToHost)) != cudaSuccess) {
+        if ((e = cudaMemcpyAsync(&word, dev.scratch, sizeof(word), cudaMemcpyDeviceToHost, stream)) != cudaSuccess ||
+            (e = cudaStreamSynchronize(stream)) != cudaSuccess) {
             return (int)e;
         }
         if (word != 0) {
-            cudaMemset(dev.scratch, 0, sizeof(word));
-            return SPORK_ERR_DEVICE_TIMEOUT;
+            cudaMemsetAsync(dev.scratch, 0, sizeof(word), stream);
+            cudaStreamSynchronize(stream);
+            return (word >> 28) == 0xCu ? SPORK_ERR_DEVICE_CHECK : SPORK_ERR_DEVICE_TIMEOUT;
         }
         return 0;
     }
@@ -1114,8 +1229,12 @@ static bool plan_from_args(spork::gemm_sm100::Params& p, uint32_t& groups, uint3
                            int block_n, int cta_group, int split_k, int max_ctas, int sm_count, int tf32)
 {
     if ((block_n != 64 && block_n != 128 && block_n != 256 && block_n != 512) || (cta_group != 1 && cta_group != 2) ||
-        (block_n == 512 && (cta_group != 2 || split_k == -1)) || split_k < -1 || max_ctas < 0 || sm_count < cta_group) {
+        (block_n == 512 && (cta_group != 2 || split_k == -1)) || max_ctas < 0 || sm_count < cta_group) {
         return false;
+    }
+    const bool split_inner = split_k <= -2;
+    if (split_inner) {
+        split_k = -split_k;
     }
     if (split_k == 0) {
         split_k = (int)spork::gemm_sm100::choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n,
@@ -1124,6 +1243,7 @@ static bool plan_from_args(spork::gemm_sm100::Params& p, uint32_t& groups, uint3
     spork::gemm_sm100::plan_launch(p, groups, M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n,
                                    (uint32_t)cta_group, tf32 ? 32u : 64u, split_k == -1 ? 1u : (uint32_t)split_k,
                                    split_k == -1, max_ctas, sm_count);
+    p.split_inner = split_inner ? 1u : 0u;
     p.group_m = (uint32_t)spork::gemm_sm100::kGroupM;
     return true;
 }
@@ -1206,6 +1326,16 @@ extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int 
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
     spork::gemm_sm100::g_tuning.l2_hints = l2_hints;
     spork::gemm_sm100::g_tuning.backoff_ns = backoff_ns;
+    return 0;
+}
+
+extern "C" int spork_gemm_sm100_tmap_cache_stats(uint64_t* hits, uint64_t* misses)
+{
+    if (!hits || !misses) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    *hits = spork::gemm_sm100::g_tmap_hits.load();
+    *misses = spork::gemm_sm100::g_tmap_misses.load();
     return 0;
 }
 

@@ -15,10 +15,12 @@
 // ring depth (4 stages of 48 KB).
 //
 // The epilogue warps (8) copy a half accumulator from tensor memory into registers in one go
-// (128 fp32 per thread), release the columns at once, and only then write the registers out: the
-// tensor pipe waits for the copy into registers, not for the stores.  The registers of one half must
-// be out before the other half can be taken, so the write-out (a swizzled shared-memory slab per warp
-// and TMA stores) is on the critical path at the tile ends.
+// (128 fp32 per thread) and release the columns at once: the tensor pipe waits for the copy into
+// registers, not for the stores.  H0 is then written out (a swizzled shared-memory slab per warp and
+// TMA stores) 32 columns at a time, and the registers each chunk frees take the same chunk of H1, so
+// H1's columns are released as H0's last store is issued.  Measured on CTA 0 (spork_gemm_sm100_trace),
+// 8192^3 at 1.4 GHz: copy of a half 1000-3000 cycles (slow while MMAs run: they own the tensor-memory
+// bandwidth), write-out of a half 3200-4000 cycles.
 //
 // Same operand layout, tensor maps, work-item list, raster and bounded waits as gemm_kernel.
 #pragma once
@@ -31,7 +33,7 @@ constexpr int kWideN = 2 * kWideHalfN;        // columns of a tile
 constexpr int kWideEpiWarps = 8;
 constexpr int kWideThreads = 32 * (2 + kWideEpiWarps);
 constexpr int kWideStages = 4;
-constexpr int kWideGroupM = 8;
+constexpr int kWideGroupM = 12;   // raster group (m-tiles); 8 / 12 / 16 measured within 1 % of each other
 
 struct WideConfig {
     static constexpr int kABytes = kBlockM * kBlockK * 2;               // this CTA's 128 rows of A
@@ -105,6 +107,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tcgen05_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
+    const Checker chk{p.status, smem_base, smem_u32(smem_raw) + (uint32_t)Cfg::kSmemBytes, tmem_base,
+                      (uint32_t)Cfg::kTmemCols};
+    constexpr uint32_t kOperandBytes = kTf32 ? 4u : 2u;
+
     // set-up done: from here on global memory is touched, so the previous kernel in the stream must be
     // complete (see gemm_kernel)
     grid_launch_dependents();
@@ -143,6 +149,12 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     const uint32_t leader_full = map_to_cta(full, 0);
                     const int32_t x = (int32_t)(kb * kElemsK);
+                    if (!(chk.smem(sa, Cfg::kStageBytes, 1024u, 0x11) && chk.tma_coords(x, kOperandBytes, a_row, 0, 0x12) &&
+                          chk.tma_coords(x, kOperandBytes, b_row + kWideHalfN, 0, 0x13))) {
+                        *abort_flag = 1u;
+                        ok = false;
+                        break;
+                    }
                     tma_load_2d_pair_hint(sa, &tmap_a, leader_full, x, a_row, pol_a);
                     tma_load_2d_pair_hint(sb, &tmap_b, leader_full, x, b_row, pol_b);
                     tma_load_2d_pair_hint(sb + Cfg::kBHalfBytes, &tmap_b, leader_full, x, b_row + kWideHalfN, pol_b);
@@ -204,6 +216,11 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                 tcgen05_fence_after();
                             }
                             const uint32_t sa = ring_base + s * Cfg::kStageBytes;
+                            if (!(chk.smem(sa, Cfg::kStageBytes, 1024u, 0x21) && chk.tmem(tmem_d, kWideHalfN, 0x22))) {
+                                *abort_flag = 1u;
+                                ok = false;
+                                break;
+                            }
                             if (elected) {
                                 const uint64_t desc_a = umma_desc_kmajor_sw128(sa);
                                 const uint64_t desc_b = umma_desc_kmajor_sw128(sa + Cfg::kABytes + h * Cfg::kBHalfBytes);
@@ -251,7 +268,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t quarter = warp % 4;                       // TMEM lanes [32*quarter, +32) belong to this warp
         const uint32_t part = (warp - kEpilogueWarp0) / 4;       // which 128 of a half's 256 columns
         const uint32_t slab = staging_base + (warp - kEpilogueWarp0) * kSlabBytes;
-        bool ok = true;
+        bool ok = chk.smem(slab, kSlabBytes, 1024u, 0x32);
+        uint32_t r[4][32];   // 128 accumulator columns of this thread's row
         for (uint32_t item = 0; item < num_items && ok; ++item) {
             const WorkItem w = group_item(p, group_id, num_groups, item);
             const uint32_t tile_phase = item & 1u;
@@ -259,27 +277,26 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool rows_live = row0 < p.M && w.kb_begin < w.kb_end;
             const bool tracing = p.trace != nullptr && blockIdx.x == 0 && warp == kEpilogueWarp0 && lane == 0 &&
                                  item < p.trace_items;
-#pragma unroll 1
-            for (uint32_t h = 0; h < 2; ++h) {
+            const uint32_t taddr0 = tmem_base + ((quarter * 32u) << 16) + part * 128u;  // + h * 256 + c * 32
+            const uint32_t col_base = w.n_tile * kWideN + part * 128u;                    // + h * 256 + c * 32
+
+            // half `h` is final: a stamp, and the acquire side of the hand-over
+            auto wait_full = [&](uint32_t h) {
                 if (!mbar_wait(smem_u32(&bars->tmem_full[h]), tile_phase, abort_flag, p.backoff_ns)) {
                     if (lane == 0) {
                         report_timeout(p, abort_flag, 3, 0x40 + h);
                     }
-                    ok = false;
-                    break;
+                    return false;
                 }
                 tcgen05_fence_after();
                 if (tracing) {
                     p.trace[8 * item + 2 + 3 * h] = (unsigned long long)clock64();  // [2], [5]: the half was final
                 }
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + h * kWideHalfN + part * 128u;
-                uint32_t r[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld_32x32b_x32(taddr + c * kEpiCols, r[c]);
-                }
+                return chk.tmem(taddr0 + h * kWideHalfN, 4 * kEpiCols, 0x31);
+            };
+            // every column of half `h` sits in registers: the issuer may overwrite it
+            auto release = [&](uint32_t h) {
                 tmem_ld_wait();
-                // the columns are free again as soon as they sit in registers
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) {
@@ -288,78 +305,135 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (tracing) {
                     p.trace[8 * item + 3 + 3 * h] = (unsigned long long)clock64();  // [3], [6]: it sits in registers
                 }
-                const uint32_t col0 = w.n_tile * kWideN + h * kWideHalfN + part * 128u;
+            };
+            // chunk c (32 columns) of half h: registers -> slab -> TMA store (or reduce-add, or guarded scalar stores)
+            auto store_chunk = [&](uint32_t h, int c) {
+                const uint32_t col = col_base + h * kWideHalfN + c * kEpiCols;
+                if (!rows_live || col >= p.N || (p.experiment & 1u)) {
+                    return;  // warp-uniform
+                }
+                if (p.use_tma_store && !w.reduce && (p.experiment & 8u)) {
+                    // Diagnostic alternative to the TMA stores below (same results): plain stores, made
+                    // whole 128-byte lines by a turn through the slab.  Eight lanes write one row of the
+                    // slab (128 bytes), four rows per instruction.  Measured slower than the TMA stores
+                    // on every shape, at the power limit and off it.
+                    __syncwarp();
+                    const uint32_t row_addr = slab + lane * 128u;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t col = col0 + c * kEpiCols;
-                    if (!rows_live || col >= p.N || (p.experiment & 1u)) {
-                        continue;  // warp-uniform
+                    for (int j = 0; j < 8; ++j) {
+                        st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
+                                     r[c][4 * j + 2], r[c][4 * j + 3]);
                     }
-                    if (p.use_tma_store && !w.reduce && (p.experiment & 8u)) {
-                        // Diagnostic alternative to the TMA stores below (same results): plain stores, made
-                        // whole 128-byte lines by a turn through the slab.  Eight lanes write one row of the
-                        // slab (128 bytes), four rows per instruction.  Measured slower than the TMA stores
-                        // on every shape, at the power limit and off it.
-                        __syncwarp();
-                        const uint32_t row_addr = slab + lane * 128u;
+                    __syncwarp();
+                    const uint32_t sub_row = lane >> 3, piece = lane & 7u;
+                    const uint32_t gcol = col + piece * 4u;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
-                                         r[c][4 * j + 2], r[c][4 * j + 3]);
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t srow = 4u * i + sub_row;
+                        const uint4 v = ld_shared_v4(slab + srow * 128u + ((piece ^ (srow & 7u)) << 4));
+                        const uint32_t grow = row0 + srow;
+                        if (grow < p.M && gcol < p.N) {
+                            st_global_v4(p.C + (size_t)grow * p.N + gcol, v);
                         }
-                        __syncwarp();
-                        const uint32_t sub_row = lane >> 3, piece = lane & 7u;
-                        const uint32_t gcol = col + piece * 4u;
+                    }
+                } else if (p.use_tma_store) {
+                    if (lane == 0) {
+                        bulk_wait_group_read<0>();  // the previous store has read the slab
+                    }
+                    __syncwarp();
+                    const uint32_t row_addr = slab + lane * 128u;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const uint32_t srow = 4u * i + sub_row;
-                            const uint4 v = ld_shared_v4(slab + srow * 128u + ((piece ^ (srow & 7u)) << 4));
-                            const uint32_t grow = row0 + srow;
-                            if (grow < p.M && gcol < p.N) {
-                                st_global_v4(p.C + (size_t)grow * p.N + gcol, v);
-                            }
+                    for (int j = 0; j < 8; ++j) {
+                        st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
+                                     r[c][4 * j + 2], r[c][4 * j + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (w.reduce) {
+                            tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
+                        } else {
+                            tma_store_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
                         }
-                    } else if (p.use_tma_store) {
-                        if (lane == 0) {
-                            bulk_wait_group_read<0>();  // the previous store has read the slab
-                        }
-                        __syncwarp();
-                        const uint32_t row_addr = slab + lane * 128u;
+                        bulk_commit_group();
+                    }
+                } else {
+                    const uint32_t row = row0 + lane;
+                    if (row < p.M) {
+                        float* dst = p.C + (size_t)row * p.N + col;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            st_shared_v4(row_addr + (((uint32_t)j ^ (lane & 7u)) << 4), r[c][4 * j], r[c][4 * j + 1],
-                                         r[c][4 * j + 2], r[c][4 * j + 3]);
-                        }
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (w.reduce) {
-                                tma_reduce_add_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
-                            } else {
-                                tma_store_2d(&tmap_c, slab, (int32_t)col, (int32_t)row0);
-                            }
-                            bulk_commit_group();
-                        }
-                    } else {
-                        const uint32_t row = row0 + lane;
-                        if (row < p.M) {
-                            float* dst = p.C + (size_t)row * p.N + col;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                if (col + j < p.N) {
-                                    if (w.reduce) {
-                                        atomicAdd(dst + j, __uint_as_float(r[c][j]));
-                                    } else {
-                                        dst[j] = __uint_as_float(r[c][j]);
-                                    }
+                        for (int j = 0; j < 32; ++j) {
+                            if (col + j < p.N) {
+                                if (w.reduce) {
+                                    atomicAdd(dst + j, __uint_as_float(r[c][j]));
+                                } else {
+                                    dst[j] = __uint_as_float(r[c][j]);
                                 }
                             }
                         }
                     }
                 }
-                if (tracing) {
-                    p.trace[8 * item + 4 + 3 * h] = (unsigned long long)clock64();  // [4], [7]: its last store was issued
+            };
+
+            // H0: tensor memory -> registers, release
+            if (!wait_full(0)) {
+                ok = false;
+                break;
+            }
+            uint32_t(&r_all)[128] = *reinterpret_cast<uint32_t(*)[128]>(&r[0][0]);
+            if (p.experiment & 4u) {
+                // diagnostic variant: one 128-column load per half, no interleaving
+                tmem_ld_32x32b_x128(taddr0, r_all);
+                release(0);
+                if (!wait_full(1)) {
+                    ok = false;
+                    break;
                 }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    store_chunk(0, c);
+                }
+                if (tracing) {
+                    p.trace[8 * item + 4] = (unsigned long long)clock64();
+                }
+                tmem_ld_32x32b_x128(taddr0 + kWideHalfN, r_all);
+                release(1);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    store_chunk(1, c);
+                }
+                if (tracing) {
+                    p.trace[8 * item + 7] = (unsigned long long)clock64();
+                }
+                continue;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld_32x32b_x32(taddr0 + c * kEpiCols, r[c]);
+            }
+            release(0);
+            // H1 became final while that copy ran (it trails H0 by the skew).  Write H0 out chunk by chunk and
+            // refill each chunk's registers with H1 at once, so that H1's columns are free when H0's last store
+            // has been issued, not a second copy later.
+            if (!wait_full(1)) {
+                ok = false;
+                break;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                store_chunk(0, c);
+                tmem_ld_32x32b_x32(taddr0 + kWideHalfN + c * kEpiCols, r[c]);
+            }
+            if (tracing) {
+                p.trace[8 * item + 4] = (unsigned long long)clock64();  // [4]: H0's last store was issued
+            }
+            release(1);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                store_chunk(1, c);
+            }
+            if (tracing) {
+                p.trace[8 * item + 7] = (unsigned long long)clock64();  // [7]: H1's last store was issued
             }
         }
         if (lane == 0) {

@@ -203,8 +203,50 @@ __global__ void bounded_wait_selftest_kernel(uint32_t* status, uint64_t limit_ns
     __syncthreads();
 }
 
+// Self-test of the debug build's range checks: the checks are asked about an address, a tensor-memory
+// column and a TMA coordinate that lie outside made-up ranges.  Nothing is accessed; in a checked build
+// the first refusal lands in the status word, in a normal build the checks are compiled out.
+__global__ void range_check_selftest_kernel(uint32_t* status, int which, uint32_t* refused)
+{
+    const ptx::Checker chk{status, 0x1000u, 0x2000u, 64u, 128u};
+    bool ok = true;
+    if (which == 0) {
+        ok = chk.smem(0x1F00u, 0x200u, 16u, 0x701);           // runs past the end of the window
+    } else if (which == 1) {
+        ok = chk.tmem((32u << 16) | 160u, 64u, 0x702);         // columns 160..223 of an allocation that ends at 192
+    } else if (which == 2) {
+        ok = chk.tma_coords(12, 2u, 0, 0, 0x703);              // 24 bytes: not on a 16-byte boundary
+    } else {
+        ok = chk.smem(0x1400u, 0x100u, 1024u, 0x704) && chk.tmem(64u, 128u, 0x705) && chk.tma_coords(16, 2u, 5, 0, 0x706);
+    }
+    *refused = ok ? 0u : 1u;
+}
+
 }  // namespace harness
 }  // namespace spork
+
+extern "C" int spork_selftest_range_check(int which, void* stream)
+{
+#ifndef SPORK_CHECKED
+    (void)which;
+    (void)stream;
+    return SPORK_ERR_UNSUPPORTED_SHAPE;  // only the debug build has range checks
+#else
+    if (which < 0 || which > 3) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::DeviceState* dev = nullptr;
+    const int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    // word 15 of the 64-byte status block receives whether the check refused (read back by the caller's
+    // status query only through the status word itself)
+    spork::harness::range_check_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+        dev->status_word, which, dev->status_word + 15);
+    return (int)cudaGetLastError();
+#endif
+}
 
 extern "C" int spork_selftest_bounded_wait(uint32_t limit_us, void* stream)
 {

@@ -444,8 +444,39 @@ struct Model {
         return written[((item * 2 + a) * 2 + cta) * 8 + warp];
     }
 
+    // gemm_wide_kernel: H0 into registers, release; wait for H1; H0's stores interleaved with H1's copy into
+    // the registers they free; release; H1's stores
+    void epilogue_wide(int self, uint32_t cta, uint32_t warp)
+    {
+        for (uint32_t item = 0; item < num_items; ++item) {
+            const uint32_t parity = item & 1u;
+            for (uint32_t h = 0; h < 2; ++h) {
+                MBar& tf = tmem_full[cta][h];
+                sched->wait_until(self, [&tf, parity] { return tf.passed(parity); });
+                if (acc[h].item != item || acc[h].next_kb != acc[h].last_kb) {
+                    sched->fail(5);
+                }
+                sched->yield(self);   // the copy into registers takes time (h = 1: H0's stores run meanwhile)
+                if (acc[h].item != item || acc[h].next_kb != acc[h].last_kb) {
+                    sched->fail(5);
+                }
+                if (h == 1) {
+                    ++written_at(item, 0, cta, warp);
+                }
+                --acc[h].readers_left;
+                tmem_empty[h].arrive();
+            }
+            sched->yield(self);
+            ++written_at(item, 1, cta, warp);
+        }
+    }
+
     void epilogue(int self, uint32_t cta, uint32_t warp)
     {
+        if (wide) {
+            epilogue_wide(self, cta, warp);
+            return;
+        }
         for (uint32_t item = 0; item < num_items; ++item) {
             const uint32_t halves = wide ? 2u : 1u;
             for (uint32_t h = 0; h < halves; ++h) {

@@ -153,6 +153,20 @@ def test_split_k_reduce_add(sp, orc, cuda, split_k):
         _check(sp, orc, a, b, c, K)
 
 
+@pytest.mark.parametrize("split_k", [-2, -3, -7])
+def test_split_k_with_k_fastest_in_the_schedule(sp, orc, cuda, split_k):
+    """split_k <= -2: |split_k| K ranges whose work items are neighbours in the list, so that the ranges of
+    one tile run at the same time on different CTA groups (gemm_sm90_k_mode::split_k_inner,
+    gemm/gemm_sm90.cu:1096-1114); same sums as the K-slowest order."""
+    M, N, K = 640, 1100, 2048
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    for block_n, cta_group, max_ctas in ((128, 2, 0), (256, 1, 6), (512, 2, 4)):
+        c = _poisoned(cuda, M, N)
+        sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=cta_group, split_k=split_k, max_ctas=max_ctas)
+        sp.status()
+        _check(sp, orc, a, b, c, K)
+
+
 @pytest.mark.parametrize("shape", [(1536, 2304, 8192), (512, 512, 4096), (16384, 64, 1024), (160, 480, 816),
                                    (2048, 6000, 264), (300, 131, 2056), (256, 256, 64)])
 def test_stream_k(sp, orc, cuda, shape):
@@ -230,8 +244,8 @@ def test_argument_errors_are_returned_not_trapped(sp, cuda):
     assert L.spork_gemm_sm100_f16f32(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 100, None) == 10001
     assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 3, 1, 0,
                                         None) == 10001
-    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 2, -2, 0,
-                                        None) == 10001  # split_k: 0 = choose, -1 = stream-K, nothing below
+    assert L.spork_gemm_sm100_f16f32_ex(128, 128, 72, a.data_ptr(), b.data_ptr(), c.data_ptr(), 128, 2, 1, -1,
+                                        None) == 10001  # max_ctas cannot be negative
     with pytest.raises(TypeError):
         sp.matmul_sm100(a.float(), b)
     with pytest.raises(ValueError):
@@ -417,3 +431,27 @@ def test_launches_that_depend_on_the_previous_kernel(sp, orc, cuda, no_early_lau
     assert orc.normalised_error(c2.cpu().numpy(), ref2, float(a2.abs().max()), 1.0, K) < 1e-2
     ref3 = orc.gemm_f16f32(B, A)
     assert orc.normalised_error(c1.cpu().numpy(), ref3, 1.0, 1.0, K) < 1e-2
+
+
+def test_tensor_maps_are_encoded_once_per_operand(sp, orc, cuda):
+    """A repeated launch on the same operands makes no driver call for its three TMA descriptors; the same
+    memory viewed with another shape gets descriptors of its own (and the right answer)."""
+    import torch
+
+    M, N, K = 384, 256, 512
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c, block_n=128, cta_group=2)
+    h0, m0 = sp.tmap_cache_stats()
+    sp.matmul_sm100(a, b, c, block_n=128, cta_group=2)
+    h1, m1 = sp.tmap_cache_stats()
+    assert (h1 - h0, m1 - m0) == (3, 0)
+    sp.status()
+    _check(sp, orc, a, b, c, K)
+    # the same allocations as a 192 x 1024 and a 128 x 1024 matrix
+    a2, b2 = a.view(192, 1024), b.view(128, 1024)
+    c2 = sp.matmul_sm100(a2, b2, block_n=128, cta_group=2)
+    h2, m2 = sp.tmap_cache_stats()
+    assert m2 - m1 == 3
+    sp.status()
+    _check(sp, orc, a2, b2, c2, 1024)

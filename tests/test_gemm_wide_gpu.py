@@ -88,7 +88,7 @@ def test_library_choice_equals_the_narrow_kernel(sp, orc, cuda):
     result is the same bits."""
     import torch
 
-    M, N, K = 4864, 8192, 1024  # 19 x 16 = 304 wide tiles: more than two waves of 74 pairs
+    M, N, K = 4864, 8192, 4096  # 19 x 16 = 304 wide tiles: more than two waves of 74 pairs, and a long K
     a, b = _inputs(sp, orc, cuda, M, N, K)
     outs = []
     for wide in (0, 1, 2):

@@ -49,7 +49,7 @@ def test_split_k_is_normalised(L):
     p = _plan(L, 512, 512, 2048, 128, 2, 3)
     assert p["kb_per_split"] == 11 and p["split_k"] == 3  # 11 + 11 + 10, no empty split
     assert L.spork_gemm_sm100_plan(1, 1, 8, 100, 2, 1, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001
-    assert L.spork_gemm_sm100_plan(1, 1, 8, 128, 2, -2, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001  # 0 = choose, -1 = stream-K
+    assert L.spork_gemm_sm100_plan(1, 1, 8, 512, 2, -1, 0, 148, 0, (ctypes.c_uint32 * 10)()) == 10001  # no stream-K with 256 x 512 tiles
 
 
 @pytest.mark.parametrize("shape,bn,cg,sk,max_ctas", [
@@ -57,6 +57,9 @@ def test_split_k_is_normalised(L):
     ((160, 480, 816), 128, 1, -1, 0), ((2048, 6000, 264), 64, 2, -1, 20), ((1000, 264, 136), 256, 2, 1, 0),
     ((768, 768, 4096), 256, 1, 4, 0), ((300, 131, 2056), 128, 2, -1, 0), ((8192, 8192, 8192), 256, 2, -1, 0),
     ((4096, 4096, 64), 128, 2, 3, 6),
+    # 256 x 512 tiles, and split-K with K fastest in the schedule (gemm_sm90_k_mode::split_k_inner)
+    ((8192, 8192, 8192), 512, 2, 1, 0), ((1000, 2050, 264), 512, 2, 3, 4), ((640, 1100, 2048), 256, 1, -3, 6),
+    ((1536, 2304, 8192), 512, 2, -4, 0),
 ])
 def test_every_k_block_of_every_tile_is_covered_exactly_once(L, shape, bn, cg, sk, max_ctas):
     M, N, K = shape
@@ -77,6 +80,12 @@ def test_every_k_block_of_every_tile_is_covered_exactly_once(L, shape, bn, cg, s
         assert bool(red) == ((m, n) in reduce_tiles)
     if sk == 1:
         assert not reduce_tiles
+    if sk <= -2:
+        # K fastest: the ranges of one tile sit next to each other in the work list, i.e. on neighbouring groups
+        first = _items(L, M, N, K, bn, cg, sk, 0, max_ctas)[0]
+        if p["groups"] > 1:
+            second = _items(L, M, N, K, bn, cg, sk, 1, max_ctas)[0]
+            assert first[:2] == second[:2] and second[2] == first[3]
     if p["sk_tiles"]:
         assert len(reduce_tiles) == p["sk_tiles"]
         loads = [sum(kb1 - kb0 for (_, _, kb0, kb1, red) in _items(L, M, N, K, bn, cg, sk, g, max_ctas) if red)
