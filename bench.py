@@ -216,7 +216,7 @@ def other_configs(sp, torch, dev, peaks):
     qkv = []
     for seed in (101, 101 ^ 888, 101 ^ 1776):
         t = torch.empty((BH * S, D), dtype=torch.float16, device=dev)
-        sp.init_test_data(t, sp.DATA_NORMAL, seed)
+        sp.init_test_data(t, sp.DATA_NORMAL_BM, seed)
         qkv.append(t.view(BH, S, D))
     o = torch.empty_like(qkv[0])
     ms = iqr_ms(lambda: sp.attn_fwd(qkv[0], qkv[1], qkv[2], o), n=15)
@@ -239,7 +239,7 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
     qkv = []
     for seed in (101, 101 ^ 888, 101 ^ 1776):
         t = torch.empty((slab.count * S, D), dtype=torch.float16, device=dev)
-        sp.init_test_data(t, sp.DATA_NORMAL, seed, row0=slab.start * S)
+        sp.init_test_data(t, sp.DATA_NORMAL_BM, seed, row0=slab.start * S)
         qkv.append(t.view(slab.count, S, D))
     o = torch.empty_like(qkv[0])
     causal = bool(args.causal)
@@ -275,7 +275,7 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
                       "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                       "dtype": "f16 in, f32 softmax, f16 out", "data": "synthetic",
                       "config": {"workload": f"attention forward BH={BH_TOTAL} S=4096 D={D}, heads sharded over ranks",
-                                 "values": "unit normal from a position hash, seeds 101, 101^888, 101^1776",
+                                 "values": "N(0,1) by Box-Muller on a position hash, seeds 101, 101^888, 101^1776",
                                  "l2": "inputs exceed L2: Q,K,V,O = 1 GiB"},
                       "clocks": clocks.summary(), "gpu_launches": args.steps,
                       "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],

@@ -260,7 +260,10 @@ int spork_gemm_sm100_htod_f16f32(uint32_t M, uint32_t N, uint32_t K, const void*
 
 /* Seeded fixture fill of a rows x cols fp16 matrix; code: 0 sparse random,
  * 1 identity, 2 tiled numbers (gemm/gemm_test.cu:55-96), 3 uniform [-1,1),
- * 4 unit normal.  transpose_rule as in the reference. */
+ * 4 unit normal as a sum of twelve hashed uniforms (bit-reproducible on the
+ * host, tails end at +-6), 5 unit normal by Box-Muller (true tails; the host
+ * generator agrees statistically, not bit for bit).  transpose_rule as in the
+ * reference. */
 int spork_init_test_data_f16(void* d_tensor, uint32_t rows, uint32_t cols, int code, uint32_t seed,
                              int transpose_rule, void* stream);
 
@@ -287,7 +290,9 @@ int spork_compare_f32(const float* d_a, const float* d_b, uint32_t rows, uint32_
 /* ---- Attention forward ---------------------------------------------------
  * O = softmax(Q K^T * scale) V per head; q, k, v, o are [BH][S][D] fp16,
  * row-major, each head laid out like the reference's single (N, d) problem
- * (matrix_util.hpp:40-45); softmax in fp32.  Replaces
+ * (matrix_util.hpp:40-45); softmax in fp32.  D is 64 or 128; scale must be
+ * positive (simple_attn's default is 1 / sqrt(D), torch_attn.py:11-16; zero,
+ * negative and NaN are refused with SPORK_ERR_BAD_ARGUMENT).  Replaces
  * launch_tk_4090_fwd_kernel (tk_4090_fwd.hpp:5). */
 int spork_attn_sm100_supports(int BH, int S, int D);
 int spork_attn_sm100_fwd_f16(int BH, int S, int D, const void* q, const void* k, const void* v, void* o, float scale,

@@ -19,6 +19,7 @@ DATA_IDENTITY = 1
 DATA_TILED_NUMBERS = 2
 DATA_UNIFORM_PM1 = 3
 DATA_NORMAL = 4
+DATA_NORMAL_BM = 5  # Box-Muller unit normal: statistically, not bitwise, the device's fixture
 
 # The reference's two hash constants (gemm/gemm_test.cu:73,86) double as the
 # seeds of the A and B operands of the uniform fixtures.

@@ -162,6 +162,7 @@ enum {
     SPORK_DATA_TILED_NUMBERS = 2,
     SPORK_DATA_UNIFORM_PM1 = 3,
     SPORK_DATA_NORMAL = 4,
+    SPORK_DATA_NORMAL_BM = 5,
 };
 
 /* One fixture element at logical coordinate (x, y).
@@ -190,6 +191,15 @@ static inline uint16_t fixture_value(uint32_t x, uint32_t y, int code, uint32_t 
          * 24 significant bits, so round once through double. */
         const double v = ((double)sum - 6.0 * 16777216.0) * (1.0 / 16777216.0);
         return float_to_half_bits((float)v);
+    }
+    case SPORK_DATA_NORMAL_BM: {
+        /* Box-Muller on two hashed 24-bit uniforms, as the device generator does; the C library's logf /
+         * cosf may differ from the device's in the last bit, so this code is statistically, not bitwise,
+         * the same fixture (parity tests read the device's bits back instead). */
+        const uint64_t h = spork_oracle_pcg3d(x, y, seed);
+        const float u1 = ((float)(uint32_t)(h & 0xFFFFFFu) + 1.0f) * (1.0f / 16777216.0f);
+        const float u2 = (float)(uint32_t)((h >> 24) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+        return float_to_half_bits(sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2));
     }
     case SPORK_DATA_RANDOM:
     default: {

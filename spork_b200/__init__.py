@@ -10,6 +10,7 @@ or the device is not a B200-class GPU.
 from .api import (  # noqa: F401
     DATA_IDENTITY,
     DATA_NORMAL,
+    DATA_NORMAL_BM,
     DATA_RANDOM,
     DATA_TILED_NUMBERS,
     DATA_UNIFORM_PM1,

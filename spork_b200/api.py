@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.environ.get("SPORK_B200_LIBRARY") or os.path.join(_HERE, "libspork_b200.so")
 
 # Fixture codes of init_test_data: 0..2 are the reference's TestDataCode (gemm/gemm_test.h:6-11).
-DATA_RANDOM, DATA_IDENTITY, DATA_TILED_NUMBERS, DATA_UNIFORM_PM1, DATA_NORMAL = range(5)
+DATA_RANDOM, DATA_IDENTITY, DATA_TILED_NUMBERS, DATA_UNIFORM_PM1, DATA_NORMAL, DATA_NORMAL_BM = range(6)
 # The reference's two hash constants (gemm/gemm_test.cu:73,86) seed the A and B operands.
 SEED_A = 20010106
 SEED_B = 19980724

@@ -64,6 +64,41 @@ def build(force: bool = False, verbose: bool = False, checked: bool = False) -> 
     return lib
 
 
+CUTLASS_COLUMN = os.path.join(HERE, "bin", "libcutlass_column.so")
+
+
+def find_cutlass() -> str | None:
+    """A CUTLASS header tree for the harness's comparison column: $SPORK_CUTLASS_DIR, or the copy some
+    Python packages ship in their data directory.  None if there is none (the column is then absent)."""
+    import importlib.util
+
+    cands = [os.environ.get("SPORK_CUTLASS_DIR")]
+    for pkg, sub in (("flashinfer", os.path.join("data", "cutlass")),):
+        spec = importlib.util.find_spec(pkg)
+        if spec and spec.submodule_search_locations:
+            cands.append(os.path.join(list(spec.submodule_search_locations)[0], sub))
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "include", "cutlass", "cutlass.h")):
+            return c
+    return None
+
+
+def build_cutlass_column() -> str | None:
+    """Compile csrc/main_cutlass_column.cu into bin/libcutlass_column.so (about a minute); the harness loads it
+    at run time when it exists.  Returns None where no CUTLASS headers are installed."""
+    root = find_cutlass()
+    if root is None:
+        return None
+    src = os.path.join(CSRC, "main_cutlass_column.cu")
+    os.makedirs(os.path.dirname(CUTLASS_COLUMN), exist_ok=True)
+    if _stale(CUTLASS_COLUMN, [src]):
+        cmd = [NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr",
+               "-diag-suppress", "20012", "-I", os.path.join(root, "include"), "-I", os.path.join(root, "tools", "util", "include"),
+               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared", "-o", CUTLASS_COLUMN, src]
+        subprocess.run(cmd, check=True)
+    return CUTLASS_COLUMN
+
+
 def build_harness() -> str:
     """Link the C++ benchmark/correctness harness (csrc/main_gemm.cpp) against the library and cuBLAS."""
     build()
@@ -71,7 +106,7 @@ def build_harness() -> str:
     os.makedirs(os.path.dirname(exe), exist_ok=True)
     src = os.path.join(CSRC, "main_gemm.cpp")
     if _stale(exe, [src, LIB, os.path.join(HERE, "..", "include", "gemm_sm100.h")]):
-        cmd = [NVCC, "-std=c++17", "-O2", "-x", "cu", src, "-o", exe, "-L", HERE, "-lspork_b200", "-lcublas",
+        cmd = [NVCC, "-std=c++17", "-O2", "-x", "cu", src, "-o", exe, "-L", HERE, "-lspork_b200", "-lcublas", "-ldl",
                "-Xlinker", "-rpath=$ORIGIN/.."]
         subprocess.run(cmd, check=True)
     return exe
@@ -81,3 +116,5 @@ if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv))
     if "--harness" in sys.argv:
         print(build_harness())
+    if "--cutlass" in sys.argv:
+        print(build_cutlass_column() or "no CUTLASS headers found: the harness runs without that column")

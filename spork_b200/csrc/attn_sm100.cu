@@ -170,7 +170,14 @@ constexpr float kPolyLo = 56.0f;
 // How many of every eight pairs of exponentials take that route. Measured at B*H = 256, S = 4096, D = 128,
 // interleaved runs on a part warmed into its power cap: 0 -> 1099, 1 -> 1145, 2 -> 1163, 3 -> 1173,
 // 4 -> 1069 TFLOP/s (cold: 1264, 1281, 1173, 1193, 1112).
-constexpr int kPolyPairs = 3;
+#ifndef SPORK_ATTN_POLY_PAIRS_D128
+#define SPORK_ATTN_POLY_PAIRS_D128 3
+#endif
+#ifndef SPORK_ATTN_POLY_PAIRS_D64
+#define SPORK_ATTN_POLY_PAIRS_D64 3
+#endif
+template <int D>
+constexpr int kPolyPairs = D == 64 ? SPORK_ATTN_POLY_PAIRS_D64 : SPORK_ATTN_POLY_PAIRS_D128;
 __device__ __forceinline__ void ex2_poly2(float s0, float s1, float ks, float cs, float& p0, float& p1)
 {
     const uint64_t y = pack2(fma_sat(s0, ks, cs), fma_sat(s1, ks, cs));
@@ -569,7 +576,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     const float s0 = __uint_as_float(r[half * 64 + 2 * i]);
                     const float s1 = __uint_as_float(r[half * 64 + 2 * i + 1]);
                     float p0, p1;
-                    if ((i & 7) < kPolyPairs) {
+                    if ((i & 7) < kPolyPairs<D>) {
                         ex2_poly2(s0, s1, ks, cs, p0, p1);
                     } else {
                         float x0, x1;
@@ -747,7 +754,10 @@ static int attn_dispatch(int BH, int S, int D, const void* q, const void* k, con
         return 0;
     }
     auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
-    if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !(scale >= 0.0f)) {
+    // scale must be positive: the kernel folds it into the exponent ((s - max) * scale * log2 e), and with
+    // scale = 0 the -inf of a masked score would meet a zero factor (NaN).  Negative or NaN scales are
+    // refused as well.
+    if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !(scale > 0.0f)) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     spork::DeviceState* dev = nullptr;

@@ -542,32 +542,26 @@ struct TmapKey {
 };
 
 struct TmapCache {
-    static constexpr int kSlots = 64;  // direct mapped
+    static constexpr int kSlots = 32;  // searched linearly; replaced round-robin
     struct Slot {
         bool valid = false;
         TmapKey key{};
         CUtensorMap map;
     };
     Slot slots[kSlots];
-    uint64_t hits = 0, misses = 0;
-    static uint32_t slot_of(const TmapKey& k)
-    {
-        uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
-        h ^= (k.rows * 0xC2B2AE3D27D4EB4Full) ^ (k.cols * 0x165667B19E3779F9ull) ^ (k.batches << 40) ^
-             ((uint64_t)k.box_rows << 20) ^ ((uint64_t)k.box_cols << 8) ^ k.dtype ^ ((uint64_t)k.dims << 4);
-        return (uint32_t)((h >> 32) % kSlots);
-    }
+    int next = 0;
 };
 static thread_local TmapCache t_tmap_cache;
 static std::atomic<uint64_t> g_tmap_hits{0}, g_tmap_misses{0};
 
 static bool tmap_lookup(const TmapKey& key, CUtensorMap* map)
 {
-    const TmapCache::Slot& s = t_tmap_cache.slots[TmapCache::slot_of(key)];
-    if (s.valid && s.key == key) {
-        *map = s.map;
-        g_tmap_hits.fetch_add(1, std::memory_order_relaxed);
-        return true;
+    for (const TmapCache::Slot& s : t_tmap_cache.slots) {
+        if (s.valid && s.key == key) {
+            *map = s.map;
+            g_tmap_hits.fetch_add(1, std::memory_order_relaxed);
+            return true;
+        }
     }
     g_tmap_misses.fetch_add(1, std::memory_order_relaxed);
     return false;
@@ -575,7 +569,9 @@ static bool tmap_lookup(const TmapKey& key, CUtensorMap* map)
 
 static void tmap_remember(const TmapKey& key, const CUtensorMap& map)
 {
-    TmapCache::Slot& s = t_tmap_cache.slots[TmapCache::slot_of(key)];
+    TmapCache& c = t_tmap_cache;
+    TmapCache::Slot& s = c.slots[c.next];
+    c.next = (c.next + 1) % TmapCache::kSlots;
     s.valid = true;
     s.key = key;
     s.map = map;
@@ -788,7 +784,7 @@ static int launch_wide(uint32_t M, uint32_t N, uint32_t K, const void* A, const 
     p.group_m = tune.wide_group_m >= 1 ? (uint32_t)tune.wide_group_m : (uint32_t)kWideGroupM;
     p.l2_hints = effective_l2_hints(tune.l2_hints);
     p.backoff_ns = (uint32_t)tune.backoff_ns;
-    p.experiment = (uint32_t)tune.experiment & 13u;
+    p.experiment = (uint32_t)tune.experiment & 9u;
     p.wide_skew = tune.wide_skew >= 1 ? (uint32_t)tune.wide_skew : (uint32_t)kWideStages;
     p.trace = tune.trace;
     p.trace_items = tune.trace_items;
@@ -939,6 +935,11 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     const bool wide_k = !tf32 && (g_tuning.k_atoms == 2 ||
                                   (cta_group == 2 && g_tuning.k_atoms == 0 && block_n <= 128 &&
                                    out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
+    if (!tf32 && g_tuning.k_atoms == 3 && cta_group == 2 && block_n <= 128) {
+        // four column blocks (512 contiguous bytes per row and request): an experiment for the skinny shapes
+        return block_n == 64 ? launch<2, 64, false, 4>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner)
+                             : launch<2, 128, false, 4>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
+    }
     if (wide_k && cta_group == 2) {
         switch (block_n) {
         case 64: return launch<2, 64, false, 2>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner);
@@ -1311,7 +1312,7 @@ extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x1FFFFFF || ((l2_hints >> 8) & 3) > 2 ||
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x1FFFFFF || 
         ((l2_hints >> 10) & 3) > 2 || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }

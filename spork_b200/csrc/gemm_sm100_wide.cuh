@@ -19,8 +19,9 @@
 // registers, not for the stores.  H0 is then written out (a swizzled shared-memory slab per warp and
 // TMA stores) 32 columns at a time, and the registers each chunk frees take the same chunk of H1, so
 // H1's columns are released as H0's last store is issued.  Measured on CTA 0 (spork_gemm_sm100_trace),
-// 8192^3 at 1.4 GHz: copy of a half 1000-3000 cycles (slow while MMAs run: they own the tensor-memory
-// bandwidth), write-out of a half 3200-4000 cycles.
+// 8192^3 at 1.4 GHz: copy of a half 2800 cycles while operand loads and MMAs run (1100 on the last tile,
+// when no loads are in flight; one 128-column load instruction or four of 32 columns make no difference),
+// write-out of a half 3500-4000 cycles; the tensor pipe idles about 4500 cycles per 135,000-cycle tile.
 //
 // Same operand layout, tensor maps, work-item list, raster and bounded waits as gemm_kernel.
 #pragma once
@@ -379,33 +380,6 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!wait_full(0)) {
                 ok = false;
                 break;
-            }
-            uint32_t(&r_all)[128] = *reinterpret_cast<uint32_t(*)[128]>(&r[0][0]);
-            if (p.experiment & 4u) {
-                // diagnostic variant: one 128-column load per half, no interleaving
-                tmem_ld_32x32b_x128(taddr0, r_all);
-                release(0);
-                if (!wait_full(1)) {
-                    ok = false;
-                    break;
-                }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    store_chunk(0, c);
-                }
-                if (tracing) {
-                    p.trace[8 * item + 4] = (unsigned long long)clock64();
-                }
-                tmem_ld_32x32b_x128(taddr0 + kWideHalfN, r_all);
-                release(1);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    store_chunk(1, c);
-                }
-                if (tracing) {
-                    p.trace[8 * item + 7] = (unsigned long long)clock64();
-                }
-                continue;
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {

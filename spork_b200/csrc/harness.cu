@@ -36,7 +36,7 @@ __host__ __device__ inline uint64_t pcg3d(uint32_t x, uint32_t y, uint32_t z)
 // reference's three (gemm/gemm_test.cu:66-91) rounded once to fp16; 3 is
 // uniform [-1,1) from 24 hashed bits; 4 is a unit normal built as the
 // Irwin-Hall sum of twelve hashed uniforms, integer arithmetic throughout so
-// the host generator reproduces it bit for bit.
+// the host generator reproduces it bit for bit; 5 is a Box-Muller unit normal.
 __device__ inline __half fixture_value(uint32_t x, uint32_t y, int code, uint32_t seed)
 {
     switch (code) {
@@ -55,6 +55,15 @@ __device__ inline __half fixture_value(uint32_t x, uint32_t y, int code, uint32_
         }
         const double v = (double(sum) - 6.0 * 16777216.0) * (1.0 / 16777216.0);
         return __float2half_rn(float(v));
+    }
+    case 5: {
+        // a true unit normal (Box-Muller on two hashed 24-bit uniforms) for the attention configuration,
+        // whose inputs are N(0,1): unlike code 4 its tails are unbounded.  Not bit-reproducible on the host
+        // (logarithm and cosine differ in their last bits between libraries): tests read the device's bits back.
+        const uint64_t h = pcg3d(x, y, seed);
+        const float u1 = __fmul_rn(float(uint32_t(h & 0xFFFFFFu)) + 1.0f, 1.0f / 16777216.0f);  // (0, 1]
+        const float u2 = __fmul_rn(float(uint32_t((h >> 24) & 0xFFFFFFu)), 1.0f / 16777216.0f);  // [0, 1)
+        return __float2half_rn(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2));
     }
     default: {
         const uint64_t randbits = pcg3d(x, y, 20010106u);
@@ -275,7 +284,7 @@ extern "C" int spork_init_test_data_f16_at(void* d_tensor, uint32_t rows, uint32
     if (rows == 0 || cols == 0) {
         return 0;
     }
-    if (!d_tensor || code < 0 || code > 4) {
+    if (!d_tensor || code < 0 || code > 5) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
     dim3 block{16, 16, 1};

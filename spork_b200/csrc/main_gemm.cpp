@@ -19,12 +19,14 @@
 #include <cublas_v2.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <string>
 #include <vector>
 
 #include "../../include/gemm_sm100.h"
@@ -41,8 +43,9 @@ enum class AlgorithmCode {
     mine_sm_100_stream_k,
     mine_sm_100_auto_k,
     mine_sm_100_wide,
+    cutlass_sm100,
 };
-constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::mine_sm_100_wide);
+constexpr uint32_t algorithm_count = 1u + static_cast<uint32_t>(AlgorithmCode::cutlass_sm100);
 
 inline uint32_t algorithm_code_bit(AlgorithmCode code) { return 1u << static_cast<uint32_t>(code); }
 
@@ -58,6 +61,7 @@ inline const char* algorithm_name(AlgorithmCode code)
     case AlgorithmCode::mine_sm_100_stream_k: return "mine_sm_100 (stream k)";
     case AlgorithmCode::mine_sm_100_auto_k: return "mine_sm_100 (automatic k)";
     case AlgorithmCode::mine_sm_100_wide: return "mine_sm_100 (256x512 tiles)";
+    case AlgorithmCode::cutlass_sm100: return "cutlass sm100 (f16 in, f32 out, 256x256x64 pairs)";
     }
     return "unknown";
 }
@@ -75,6 +79,7 @@ inline const char* algorithm_key(AlgorithmCode code)
     case AlgorithmCode::mine_sm_100_stream_k: return "stream_k";
     case AlgorithmCode::mine_sm_100_auto_k: return "auto_k";
     case AlgorithmCode::mine_sm_100_wide: return "mine_wide";
+    case AlgorithmCode::cutlass_sm100: return "cutlass";
     }
     return "";
 }
@@ -84,6 +89,33 @@ struct TestParams {
     TestDataCode test_data_code_A, test_data_code_B;
     uint32_t algorithm_code_bits;
 };
+
+// The CUTLASS comparison column lives in a shared object of its own (bin/libcutlass_column.so, built only
+// where CUTLASS headers are installed) and is looked for beside this executable: cutlass_enabled(), like
+// the reference's (gemm/cutlass_gemm.h:6), says whether the column exists.
+typedef int (*CutlassGemmFn)(uint32_t, uint32_t, uint32_t, const void*, const void*, float*, void*, size_t, cudaStream_t);
+typedef size_t (*CutlassWorkspaceFn)(uint32_t, uint32_t, uint32_t);
+static CutlassGemmFn g_cutlass_gemm = nullptr;
+static CutlassWorkspaceFn g_cutlass_workspace = nullptr;
+
+static bool cutlass_enabled()
+{
+    static bool looked = false;
+    if (!looked) {
+        looked = true;
+        Dl_info info;
+        if (dladdr(reinterpret_cast<void*>(&cutlass_enabled), &info) && info.dli_fname) {
+            std::string dir(info.dli_fname);
+            const size_t slash = dir.rfind('/');
+            dir = slash == std::string::npos ? std::string(".") : dir.substr(0, slash);
+            if (void* h = dlopen((dir + "/libcutlass_column.so").c_str(), RTLD_NOW | RTLD_LOCAL)) {
+                g_cutlass_gemm = reinterpret_cast<CutlassGemmFn>(dlsym(h, "cutlass_sm100_f16f32"));
+                g_cutlass_workspace = reinterpret_cast<CutlassWorkspaceFn>(dlsym(h, "cutlass_sm100_workspace_bytes"));
+            }
+        }
+    }
+    return g_cutlass_gemm != nullptr && g_cutlass_workspace != nullptr;
+}
 
 static int g_failures = 0;
 static FILE* g_json = nullptr;
@@ -144,6 +176,12 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
     CUDA_OK(cudaMallocAsync(&d_c_baseline, sizeof(float) * c_elems, stream));
     CUDA_OK(cudaMallocAsync(&d_c_tested, sizeof(float) * c_elems, stream));
     CUDA_OK(cudaMallocAsync(&d_cmp, 2 * sizeof(uint64_t), stream));
+    void* d_cutlass_ws = nullptr;
+    size_t cutlass_ws_bytes = 0;
+    if ((params.algorithm_code_bits & g_algorithm_mask & algorithm_code_bit(AlgorithmCode::cutlass_sm100)) && cutlass_enabled()) {
+        cutlass_ws_bytes = g_cutlass_workspace(params.M, params.N, params.K);
+        CUDA_OK(cudaMallocAsync(&d_cutlass_ws, cutlass_ws_bytes, stream));
+    }
 
     // A is M x K; B is the logical K x N matrix stored transposed (N x K), as the reference's d_bCol.
     spork_init_test_data_f16(d_a, params.M, params.K, (int)params.test_data_code_A, 20010106u, 0, stream);
@@ -209,6 +247,10 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
             case AlgorithmCode::mine_sm_100_wide:
                 launch_rc |= matmul_sm100(t, stream, gemm_sm100_k_mode::output_stationary, 1, 512);
                 break;
+            case AlgorithmCode::cutlass_sm100:
+                launch_rc |= g_cutlass_gemm(params.M, params.N, params.K, d_a, d_bCol, d_c_tested, d_cutlass_ws,
+                                            cutlass_ws_bytes, stream);
+                break;
             }
             CUDA_OK(cudaEventRecord(test_events[test_i + 1], stream));
         }
@@ -265,6 +307,9 @@ static void gemm_test(TestParams params, cudaStream_t stream, cublasHandle_t cub
     cudaFreeAsync(d_c_baseline, stream);
     cudaFreeAsync(d_c_tested, stream);
     cudaFreeAsync(d_cmp, stream);
+    if (d_cutlass_ws) {
+        cudaFreeAsync(d_cutlass_ws, stream);
+    }
     CUDA_OK(cudaStreamSynchronize(stream));
 }
 
@@ -322,6 +367,7 @@ int main(int argc, char** argv)
     CUDA_OK(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
     const bool is_b200 = cc_major == 10;
     fprintf(stderr, "is_b200: %i\n", is_b200);
+    fprintf(stderr, "cutlass_enabled: %i\n", cutlass_enabled());
     if (!is_b200) {
         fprintf(stderr, "this harness needs an sm_100 device\n");
         return 2;
@@ -341,6 +387,9 @@ int main(int argc, char** argv)
         params.N = N;
         params.K = K;
         params.algorithm_code_bits = algorithm_code_bit(AlgorithmCode::cublas_f16);
+        if (cutlass_enabled() && M % 4 == 0 && N % 4 == 0 && K % 8 == 0) {  // the alignments its instantiation asks for
+            params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::cutlass_sm100);
+        }
         GPU_TensorsF16 t{M, N, K, nullptr, nullptr, nullptr, 0, 1, 0};
         if (matmul_sm100_supports(t)) {
             params.algorithm_code_bits |= algorithm_code_bit(AlgorithmCode::mine_sm_100);

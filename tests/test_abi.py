@@ -51,6 +51,18 @@ def test_supports_and_argument_errors_need_no_gpu(sp):
     assert "sm_100a" in sp.version()
 
 
+def test_attention_refuses_a_scale_that_is_not_positive(sp):
+    """scale = 0 (the mean of V in the reference's simple_attn) cannot be computed by a kernel that folds the
+    scale into the exponent; it is refused like a negative or NaN scale, before anything is launched."""
+    import ctypes
+
+    L = sp.lib()
+    fake = ctypes.c_void_p(0x10000)  # aligned, never dereferenced: the argument check comes first
+    for scale in (0.0, -1.0, float("nan")):
+        assert L.spork_attn_sm100_fwd_f16(1, 128, 64, fake, fake, fake, fake, ctypes.c_float(scale), None) == 10001
+    assert L.spork_attn_sm100_fwd_f16(1, 128, 96, fake, fake, fake, fake, ctypes.c_float(1.0), None) == 10002  # head dimension
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     import spork_b200.api as api
 

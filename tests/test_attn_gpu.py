@@ -22,14 +22,14 @@ def _close(got, ref):
     return not bad.any(), float(np.abs(got - ref).max())
 
 
-def _qkv(sp, cuda, BH, S, D, seed=101):
+def _qkv(sp, cuda, BH, S, D, seed=101, code=None):
     import torch
 
     ts = []
     # seeds s, s^888, s^1776 as in matrix_util.hpp:53-55
     for sd in (seed, seed ^ 888, seed ^ 1776):
         t = torch.empty((BH * S, D), dtype=torch.float16, device=cuda)
-        sp.init_test_data(t, sp.DATA_NORMAL, sd)
+        sp.init_test_data(t, sp.DATA_NORMAL if code is None else code, sd)
         ts.append(t.view(BH, S, D))
     return ts
 
@@ -306,7 +306,10 @@ def test_headline_size_heads_against_the_oracle(sp, orc, cuda):
     """B*H = 256, S = 4096, D = 128 with the configuration's seeds: three heads (first, middle, last) of the
     full launch against the CPU oracle (8.6 GFLOP per head)."""
     BH, S, D = 256, 4096, 128
-    q, k, v = _qkv(sp, cuda, BH, S, D, seed=101)
+    q, k, v = _qkv(sp, cuda, BH, S, D, seed=101, code=sp.DATA_NORMAL_BM)   # N(0,1), the configuration's distribution
+    # a true normal: standard deviation one, and tails beyond what a sum of twelve uniforms can reach
+    assert abs(float(q.float().std()) - 1.0) < 0.01 and abs(float(q.float().mean())) < 0.01
+    assert float(q.float().abs().max()) > 4.5
     o = sp.attn_fwd(q, k, v)
     sp.status()
     for h in (0, 131, 255):

@@ -204,3 +204,11 @@ def test_attention_oracle_matches_torch_sdpa(orc):
     tq, tk, tv = (torch.from_numpy(x.astype(np.float32)) for x in (q, k, v))
     ref = torch.nn.functional.scaled_dot_product_attention(tq, tk, tv).numpy()
     assert np.abs(o32 - ref).max() < 5e-6
+
+
+def test_box_muller_fixture_is_a_unit_normal(orc):
+    x = orc.fill_f16(512, 1024, orc.DATA_NORMAL_BM, 101).astype(np.float64)
+    assert abs(x.mean()) < 0.01 and abs(x.std() - 1.0) < 0.01
+    assert np.abs(x).max() > 4.0          # 5e5 samples of a true normal reach past four sigma
+    y = orc.fill_f16(512, 1024, orc.DATA_NORMAL_BM, 101 ^ 888).astype(np.float64)
+    assert abs(np.corrcoef(x.ravel(), y.ravel())[0, 1]) < 0.01   # another seed, another matrix
