@@ -34,8 +34,8 @@ FLOPS_PER_STEP = 2.0 * M_PER_RANK * N_DIM * K_DIM
 BYTES_PER_STEP = 2 * M_PER_RANK * K_DIM + 2 * N_DIM * K_DIM + 4 * M_PER_RANK * N_DIM
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at this size, and the
 # committed ncu summary the figure was read from
-NCU_TRAFFIC_BYTES = 1.051e9 + 0.2535e9
-NCU_TRAFFIC_SOURCE = "profiles/gemm_kernel_8192cubed.md"
+NCU_TRAFFIC_BYTES = 828.6e6 + 236.8e6
+NCU_TRAFFIC_SOURCE = "profiles/gemm_wide_kernel_8192cubed.md"
 
 
 def measured_peaks():
@@ -525,7 +525,8 @@ def main():
                 "traffic_source": NCU_TRAFFIC_SOURCE,
                 "peak_kind": f"{peaks['source']} cuBLAS bf16 burst (sustained {peaks['bf16_tflops_sustained']})",
                 "frac_of_nominal_2250": achieved / 2250.0,
-                "kernel": "spork::gemm_sm100::gemm_kernel<2,256>", "algorithmic_bytes": BYTES_PER_STEP,
+                "kernel": "spork::gemm_sm100::gemm_wide_kernel<false> (256 x 512 tiles per CTA pair)",
+                "algorithmic_bytes": BYTES_PER_STEP,
                 "avg_launch_ms": avg_launch_ms, "min_launch_ms": min(launch_ms),
                 "sm_mhz_in_kernel": in_kernel_mhz,
                 "frac_of_peak_at_that_clock": (FLOPS_PER_STEP / (launch_ms[-1] * 1e-3) / 1e12) /
@@ -537,14 +538,15 @@ def main():
     if world == 1:
         n_long = 300
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n_long):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+        with ClockSampler(local_rank) as long_clocks:   # a quarter of a second: enough samples to mean something
+            e0.record()
+            for _ in range(n_long):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
         sp.status()
         sustained = {"steps": n_long, "value": FLOPS_PER_STEP / (e0.elapsed_time(e1) / n_long * 1e-3) / 1e12,
-                     "unit": UNIT, "sm_mhz_in_kernel": sp.last_clock_mhz()}
+                     "unit": UNIT, "sm_mhz_in_kernel": sp.last_clock_mhz(), "clocks": long_clocks.summary()}
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:

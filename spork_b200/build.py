@@ -90,6 +90,8 @@ def build_cutlass_column() -> str | None:
     if root is None:
         return None
     src = os.path.join(CSRC, "main_cutlass_column.cu")
+    if not os.path.exists(src):
+        return None
     os.makedirs(os.path.dirname(CUTLASS_COLUMN), exist_ok=True)
     if _stale(CUTLASS_COLUMN, [src]):
         cmd = [NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr",

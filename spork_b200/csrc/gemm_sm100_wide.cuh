@@ -19,9 +19,10 @@
 // registers, not for the stores.  H0 is then written out (a swizzled shared-memory slab per warp and
 // TMA stores) 32 columns at a time, and the registers each chunk frees take the same chunk of H1, so
 // H1's columns are released as H0's last store is issued.  Measured on CTA 0 (spork_gemm_sm100_trace),
-// 8192^3 at 1.4 GHz: copy of a half 2800 cycles while operand loads and MMAs run (1100 on the last tile,
-// when no loads are in flight; one 128-column load instruction or four of 32 columns make no difference),
-// write-out of a half 3500-4000 cycles; the tensor pipe idles about 4500 cycles per 135,000-cycle tile.
+// 8192^3 at 1.4 GHz: copy of a half 2000-2800 cycles (128 KB per SM at the 64 bytes per clock tensor memory
+// delivers into registers; one 128-column load instruction or four of 32 columns make no difference, nor
+// does a sleep between the polls of the waiting issuer), write-out of a half 3500-4000 cycles; the tensor
+// pipe idles about 4500 cycles per 135,000-cycle tile.
 //
 // Same operand layout, tensor maps, work-item list, raster and bounded waits as gemm_kernel.
 #pragma once
@@ -190,8 +191,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     for (uint32_t h = 0; h < 2; ++h) {
                         if (first) {
                             // the epilogue must have taken this half of the previous tile
+                            // (this wait lasts thousands of cycles at every tile end while the epilogue warps
+                            // work through the same memory-instruction queue: it may sleep between polls)
                             if (!__all_sync(0xFFFFFFFFu, mbar_wait<true>(smem_u32(&bars->tmem_empty[h]),
-                                                                         tile_phase ^ 1u, abort_flag))) {
+                                                                         tile_phase ^ 1u, abort_flag, p.backoff_ns))) {
                                 if (elected) {
                                     report_timeout(p, abort_flag, 2, 0x40 + h);
                                 }
