@@ -280,7 +280,7 @@ def run_attention(args, sp, torch, dist, dev, rank, world):
                       "clocks": clocks.summary(), "gpu_launches": args.steps,
                       "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"],
                                    "unit": UNIT, "frac": value / world / peaks["bf16_tflops"], "traffic": None,
-                                   "kernel": f"spork::attn_sm100::attn_fwd_kernel<{D}>",
+                                   "kernel": "spork::attn_sm100::attn_fwd_two_kernel<128>" if D == 128 else "spork::attn_sm100::attn_fwd_kernel<64>",
                                    "frac_of_nominal_2250": value / world / 2250.0}}), flush=True)
 
 

@@ -178,6 +178,16 @@ int spork_gemm_sm100_ring_model(uint32_t M, uint32_t N, uint32_t K, int block_n,
                                 int max_ctas, int sm_count, int stages, int skew, uint32_t seed, uint32_t group,
                                 int inject, uint64_t* stats);
 
+/* What spork_gemm_sm100_f16f32(M, N, K, ..., variant, ...) (split_k = 1) or the
+ * _ex entry (another split_k) resolves to on a device with `sm_count` SMs, without
+ * launching anything: out[0] = tile width (64 / 128 / 256, or 512 = the 256 x 512
+ * pair-tile kernel), out[1] = CTAs per tile, out[2] = 128-byte column blocks per
+ * ring stage, out[3] = K split (-1 = stream-K).  Pure arithmetic (no CUDA call).
+ * The reference fixes these choices at compile time
+ * (gemm/gemm_sm90.cu:1278-1289). */
+int spork_gemm_sm100_choice(uint32_t M, uint32_t N, uint32_t K, int variant, int split_k, int sm_count, int tf32,
+                            int* out);
+
 /* Every GEMM launch needs three TMA descriptors (tensor maps).  They are encoded
  * by the driver once per (base address, shape, tile box, element type) and host
  * thread and reused by later launches on the same operands; this returns how many

@@ -18,6 +18,7 @@ from .api import (  # noqa: F401
     SEED_B,
     SporkError,
     attn_fwd,
+    choice,
     compare_f32,
     gemm_baseline,
     init_test_data,

@@ -83,6 +83,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_ring_model.argtypes = [u32, u32, u32, i32, i32, i32, i32, i32, i32, i32, u32, u32, i32,
                                                   ctypes.POINTER(ctypes.c_uint64)]
         L.spork_gemm_sm100_ring_model.restype = i32
+        L.spork_gemm_sm100_choice.argtypes = [u32, u32, u32, i32, i32, i32, i32, ctypes.POINTER(i32)]
+        L.spork_gemm_sm100_choice.restype = i32
         L.spork_gemm_sm100_tmap_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
         L.spork_gemm_sm100_tmap_cache_stats.restype = i32
         L.spork_gemm_sm100_trace.argtypes = [vp, u32]
@@ -265,6 +267,14 @@ def ring_model(M: int, N: int, K: int, *, block_n: int = 256, cta_group: int = 2
     rc = lib().spork_gemm_sm100_ring_model(M, N, K, block_n, cta_group, split_k, max_ctas, sm_count, stages, skew, seed,
                                            group, inject, stats)
     return rc, {"items": int(stats[0]), "mma_ops": int(stats[1]), "steps": int(stats[2]), "groups": int(stats[3])}
+
+
+def choice(M: int, N: int, K: int, *, variant: int = 0, split_k: int = 1, sm_count: int = 148, tf32: bool = False) -> dict:
+    """What a launch of this shape resolves to (tile width, CTAs per tile, column blocks per stage, K split),
+    computed without a GPU (spork_gemm_sm100_choice)."""
+    out = (ctypes.c_int * 4)()
+    _check(lib().spork_gemm_sm100_choice(M, N, K, variant, split_k, sm_count, int(tf32), out), "spork_gemm_sm100_choice")
+    return {"block_n": int(out[0]), "cta_group": int(out[1]), "k_atoms": int(out[2]), "split_k": int(out[3])}
 
 
 def tmap_cache_stats() -> tuple[int, int]:

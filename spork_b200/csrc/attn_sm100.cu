@@ -112,6 +112,18 @@ struct Barriers {
     uint32_t abort_flag;
 };
 
+// the two-buffer kernel's barriers
+struct BarriersTwo {
+    uint64_t q_full;
+    uint64_t kv_full[kMaxKvStages];
+    uint64_t kv_empty[kMaxKvStages];
+    uint64_t s_full[2];
+    uint64_t p_ready[2][2];  // [query tile][key half]
+    uint64_t pv_done[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
 __device__ __forceinline__ float ex2_approx(float x)
 {
     float y;
@@ -215,6 +227,417 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
     atomicCAS(p.status, 0u, 0x90000000u | (role << 24) | ((where & 0xFFu) << 16) | (blockIdx.x & 0xFFFFu));
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The two-buffer kernel (head dimension 128): score buffer w belongs to query tile w, S_w(j+1) is issued
+// after P_w(j) V_j has consumed the buffer, both tiles walk the same key blocks (with a causal mask the
+// first tile sees its last block fully masked).  It is kept as a kernel of its own, apart from the
+// rotating-buffer kernel below that head dimension 64 uses: with everything about a tile a compile-time
+// offset its MMA issuer is a few instructions per multiply, and measured on the same box it is 4-7 %
+// faster at head dimension 128 than the general kernel run with two buffers (the kernel is sensitive to
+// the issuer's instruction count and to instruction-cache pressure on the issuer's sub-partition).
+// kBf16: Q, K, V, P and O are bfloat16 (the reference interface's type, matrix_util.hpp:40-45) instead of fp16.
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(kNumThreads, 1)
+attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const Params p)
+{
+    using Cfg = Config<D>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t warp = __shfl_sync(0xFFFFFFFFu, threadIdx.x / 32, 0);  // provably the same in all lanes
+    const uint32_t lane = threadIdx.x % 32;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;                                  // 2 Q tiles
+    const uint32_t kv_smem = q_smem + 2 * Cfg::kTileBytes;              // ring of K / V tiles
+    constexpr int kKvStages = Cfg::kKvStages;
+    BarriersTwo* bars =
+        reinterpret_cast<BarriersTwo*>(smem_raw + (kv_smem + kKvStages * Cfg::kTileBytes - smem_u32(smem_raw)));
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    // Clock probe: the last CTA notes SM cycles and wall-clock nanoseconds at both ends of its life; their
+    // ratio is the SM clock this launch really ran at late in its run (read by spork_gemm_sm100_last_clock_mhz).
+    unsigned long long* probe = reinterpret_cast<unsigned long long*>(p.status + 4);
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        probe[0] = (unsigned long long)clock64();
+        probe[1] = global_timer_ns();
+    }
+
+    const int head = blockIdx.x / p.q_pairs;
+    // causal: the pairs with the most key blocks are launched first, so the short ones fill the tail
+    const int q_pair = p.causal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
+    const int q_row0 = q_pair * 2 * kTileQ;
+    // causal: keys beyond this CTA's last query row are never needed (both tiles walk the same blocks; the
+    // first tile sees its last block fully masked)
+    const int last_row = q_row0 + 2 * kTileQ - 1 < p.S - 1 ? q_row0 + 2 * kTileQ - 1 : p.S - 1;
+    const int n_blocks = p.causal ? last_row / kTileKV + 1 : p.kv_blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(smem_u32(&bars->kv_full[s]), 1);
+            mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+        }
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(smem_u32(&bars->s_full[w]), 1);
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(smem_u32(&bars->p_ready[w][h]), kTileQ);
+            }
+            mbar_init(smem_u32(&bars->pv_done[w]), 1);
+        }
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc<1>(smem_u32(&bars->tmem_base), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    // column offsets inside the allocation
+    const uint32_t tmem_s0 = tmem_base;          // S_w at + w * 128; P_w (fp16 pairs) reuses its first 64 columns
+    const uint32_t tmem_o0 = tmem_base + 256;    // O_w at + w * 128
+
+    // The softmax keeps a whole row of 128 scores in registers and needs room beside them to overlap
+    // the exponentials' latencies; the loader and the issuer need almost none. Whole warpgroups trade.
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+        if (warp == kLoadWarp) {
+        // ---------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            const uint32_t qf = smem_u32(&bars->q_full);
+            mbar_arrive_expect_tx(qf, 2 * Cfg::kTileBytes);
+            for (int w = 0; w < 2; ++w) {
+                for (int a = 0; a < Cfg::kAtoms; ++a) {
+                    tma_load_3d(q_smem + w * Cfg::kTileBytes + a * Cfg::kAtomBytes, &tmap_q, qf, a * 64,
+                                q_row0 + w * kTileQ, head);
+                }
+            }
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = 0; t < 2 * n_blocks && ok; ++t) {
+                // tile order: K_0, V_0, K_1, V_1, ...
+                const int j = t >> 1;
+                const CUtensorMap* map = (t & 1) ? &tmap_v : &tmap_k;
+                if (!mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, abort_flag)) {
+                    report_timeout(p, abort_flag, 1, stage);
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = smem_u32(&bars->kv_full[stage]);
+                mbar_arrive_expect_tx(full, Cfg::kTileBytes);
+                for (int a = 0; a < Cfg::kAtoms; ++a) {
+                    tma_load_3d(kv_smem + stage * Cfg::kTileBytes + a * Cfg::kAtomBytes, map, full, a * 64,
+                                j * kTileKV, head);
+                }
+                if (++stage == (uint32_t)kKvStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ MMA issuer
+        // The whole warp runs the control flow and one elected lane issues. Everything an issue needs
+        // (descriptors, tensor-memory and barrier addresses) is then the same in all lanes and can live in
+        // uniform registers; issued from inside a one-lane branch each multiply cost the thread about
+        // 60 cycles, as long as the tensor core needs to execute it, and the issuer bounded the kernel.
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_qk = umma_idesc_f16_f32(kTileQ, kTileKV, false, false, kBf16);
+        constexpr uint32_t idesc_pv = umma_idesc_f16_f32(kTileQ, D, false, true, kBf16);  // B = V is N-major
+        uint32_t stage = 0, phase = 0;  // ring position of the next tile to consume
+        bool ok = true;
+        auto advance = [&]() {
+            if (++stage == (uint32_t)kKvStages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        };
+        // Descriptor low words: one per operand tile, advanced by compile-time constants per MMA
+        // (a 64-wide column block further = +1024, 16 elements along K inside a block = +2,
+        // 16 rows further down an N-major V tile = +128, all in units of 16 bytes).
+        const uint32_t q_lo0 = desc_lo_kmajor(q_smem);
+        // S_w = Q_w K^T from the K tile in ring slot `st`. (Not split along the keys: with both operands
+        // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
+        auto issue_qk = [&](int w, uint32_t st) {
+            const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
+            const uint32_t q_lo = q_lo0 + (uint32_t)w * (Cfg::kTileBytes >> 4);
+            if (leader) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (uint32_t)((kk / 4) * (Cfg::kAtomBytes >> 4) + 2 * (kk % 4));
+                    umma_f16_ss_cta1(tmem_s0 + w * 128, q_lo + off, kDescHiSw128, k_lo + off, kDescHiSw128, idesc_qk,
+                                     kk != 0 ? 1u : 0u);
+                }
+                umma_commit<1>(smem_u32(&bars->s_full[w]));
+            }
+        };
+        // O_w (+)= P_w V: A = P_w in tensor memory (16 keys = 8 packed columns per step),
+        // B = the V tile in ring slot `st` (N-major; its d-halves are one 128-row block apart);
+        // half h covers keys [64 h, 64 h + 64)
+        auto issue_pv = [&](int w, uint32_t st, bool accumulate, int h) {
+            const uint32_t v_lo = desc_lo_mnmajor(kv_smem + st * Cfg::kTileBytes, Cfg::kAtomBytes);
+            if (leader) {
+#pragma unroll
+                for (int kk = h * (kTileKV / 32); kk < (h + 1) * (kTileKV / 32); ++kk) {
+                    umma_f16_ts_cta1(tmem_o0 + w * 128, tmem_s0 + w * 128 + kk * 8, v_lo + (uint32_t)(kk * 128),
+                                     kDescHiSw128, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
+                }
+            }
+        };
+        auto commit = [&](uint64_t* bar) {
+            if (leader) {
+                umma_commit<1>(smem_u32(bar));
+            }
+        };
+        // every lane polls; a timeout is reported once
+        auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t where) {
+            const bool done = mbar_wait(smem_u32(bar), parity, abort_flag);
+            if (!done && leader) {
+                report_timeout(p, abort_flag, 2, where);
+            }
+            return __all_sync(0xFFFFFFFFu, done);
+        };
+        do {
+            if (!wait(&bars->q_full, 0, 0x20)) {
+                break;
+            }
+            // prologue: S_0(0), S_1(0)
+            if (!wait(&bars->kv_full[stage], phase, stage)) {
+                break;
+            }
+            tcgen05_fence_after();
+            issue_qk(0, stage);
+            issue_qk(1, stage);
+            commit(&bars->kv_empty[stage]);
+            advance();
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const uint32_t v_stage = stage, v_phase = phase;
+                advance();
+                const uint32_t k_stage = stage, k_phase = phase;  // K_{j+1}, if any
+                const bool more = j + 1 < n_blocks;
+                if (more) {
+                    advance();
+                }
+                // The tiles this block's multiplies read were requested long ago; make sure of them now, while
+                // the softmax is still at work, so that nothing stands between P arriving and the issue.
+                if (!wait(&bars->kv_full[v_stage], v_phase, v_stage) ||
+                    (more && !wait(&bars->kv_full[k_stage], k_phase, k_stage))) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    if (!ok) {
+                        break;
+                    }
+                    if (!wait(&bars->p_ready[w][0], (uint32_t)(j & 1), 0x30 + w)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    issue_pv(w, v_stage, j > 0, 0);  // the first 64 keys, while the softmax does the rest
+                    if (!wait(&bars->p_ready[w][1], (uint32_t)(j & 1), 0x38 + w)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    issue_pv(w, v_stage, true, 1);
+                    if (more) {
+                        issue_qk(w, k_stage);
+                    } else {
+                        commit(&bars->pv_done[w]);  // completes once: O_w is final
+                    }
+                    if (w == 1) {
+                        commit(&bars->kv_empty[v_stage]);
+                        if (more) {
+                            commit(&bars->kv_empty[k_stage]);
+                        }
+                    }
+                }
+            }
+        } while (false);
+        }
+    } else {
+        // --------------------------------------------------------------- softmax
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+        const uint32_t w = warp / 4;        // query tile of this warpgroup
+        const uint32_t quarter = warp % 4;  // TMEM lanes [32*quarter, +32)
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32u) << 16;
+        const uint32_t tmem_s = tmem_s0 + w * 128 + lane_addr;
+        const uint32_t tmem_o = tmem_o0 + w * 128 + lane_addr;
+        const float sl2 = p.scale_log2e;
+        float m_ref = -INFINITY;  // row max the stored O and l are relative to (raw scores)
+        float l_run = 0.0f;       // running row sum
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, kSoftmaxBackoffNs)) {
+                if (lane == 0) {
+                    report_timeout(p, abort_flag, 3, 0x10 + w);
+                }
+                ok = false;
+                break;
+            }
+            // A completed s_full also means every earlier MMA of the issuing thread is complete: P_w of the
+            // previous block has been consumed and O_w is not being written.
+            tcgen05_fence_after();
+            uint32_t r[128];
+            {
+                uint32_t(&r0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
+                uint32_t(&r1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
+                uint32_t(&r2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[64]);
+                uint32_t(&r3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[96]);
+                tmem_ld_32x32b_x32(tmem_s, r0);
+                tmem_ld_32x32b_x32(tmem_s + 32, r1);
+                tmem_ld_32x32b_x32(tmem_s + 64, r2);
+                tmem_ld_32x32b_x32(tmem_s + 96, r3);
+                tmem_ld_wait();
+            }
+            int valid = p.S - j * kTileKV;  // keys of this block that exist
+            bool masked = valid < kTileKV;  // uniform over the CTA
+            if (p.causal) {
+                // keys of this block this row may see: global key index <= global query index
+                const int row_global = q_row0 + (int)w * kTileQ + (int)row;
+                const int seen = row_global - j * kTileKV + 1;
+                valid = seen < valid ? seen : valid;
+                masked = masked || (j + 1) * kTileKV > q_row0 + (int)w * kTileQ + 1;  // uniform over the tile
+            }
+            if (masked) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (i >= valid) {
+                        r[i] = 0xFF800000u;  // -inf
+                    }
+                }
+            }
+            // four independent chains of three-input max
+            float m4[4] = {__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]),
+                           __uint_as_float(r[3])};
+#pragma unroll
+            for (int i = 4; i < 124; i += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    m4[c] = max3(m4[c], __uint_as_float(r[i + 2 * c]), __uint_as_float(r[i + 2 * c + 1]));
+                }
+            }
+            m4[0] = max3(m4[0], __uint_as_float(r[124]), __uint_as_float(r[125]));
+            m4[1] = max3(m4[1], __uint_as_float(r[126]), __uint_as_float(r[127]));
+            const float m_blk = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
+            // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
+            const bool grow = j == 0 || (m_blk - m_ref) * sl2 > kRescaleThreshold;
+            float alpha = 1.0f;
+            if (grow) {
+                alpha = ex2_approx((m_ref - m_blk) * sl2);  // 0 on the first block
+                m_ref = m_blk;
+            }
+            // Rescale O_w when some row of this warp moved its reference max (never on the first block).
+            // It has to be finished before the first half of P is handed over: from then on the issuer
+            // accumulates into O_w.
+            if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32b_x32(tmem_o + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    }
+                    tmem_st_32x32b_x32(tmem_o + c * 32, o);
+                }
+            }
+            const float neg_m = -m_ref * sl2;
+            const float ks = sl2 * (1.0f / 64.0f);
+            const float cs = (neg_m + kPolyLo) * (1.0f / 64.0f);
+            // packed forms where both elements of a pair take the same step: half the issue slots
+            const uint64_t sl2_2 = pack2(sl2, sl2);
+            const uint64_t neg_m2 = pack2(neg_m, neg_m);
+            uint64_t l_blk2 = pack2(0.0f, 0.0f);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float s0 = __uint_as_float(r[half * 64 + 2 * i]);
+                    const float s1 = __uint_as_float(r[half * 64 + 2 * i + 1]);
+                    float p0, p1;
+                    if ((i & 7) < kPolyPairs<D>) {
+                        ex2_poly2(s0, s1, ks, cs, p0, p1);
+                    } else {
+                        float x0, x1;
+                        unpack2(fma2(pack2(s0, s1), sl2_2, neg_m2), x0, x1);
+                        p0 = ex2_approx(x0);
+                        p1 = ex2_approx(x1);
+                    }
+                    l_blk2 = add2(l_blk2, pack2(p0, p1));
+                    packed[i] = pack_half2<kBf16>(p0, p1);
+                }
+                tmem_st_32x32b_x32(tmem_s + half * 32, packed);
+                // hand this half of P_w over: the issuer multiplies it while the other half is computed
+                tmem_st_wait();
+                tcgen05_fence_before();
+                mbar_arrive(smem_u32(&bars->p_ready[w][half]));
+            }
+            float l_blk0, l_blk1;
+            unpack2(l_blk2, l_blk0, l_blk1);
+            l_run = l_run * alpha + (l_blk0 + l_blk1);
+        }
+        // ---- epilogue: O_w / l -> fp16 -> global
+        if (ok) {
+            if (!mbar_wait(smem_u32(&bars->pv_done[w]), 0u, abort_flag, 20)) {
+                if (lane == 0) {
+                    report_timeout(p, abort_flag, 3, 0x28 + w);
+                }
+                ok = false;
+            }
+        }
+        if (ok) {
+            tcgen05_fence_after();
+            const float inv_l = 1.0f / l_run;
+            const int q_row = q_row0 + (int)w * kTileQ + (int)row;
+            uint16_t* dst = static_cast<uint16_t*>(p.o) + ((size_t)head * p.S + (size_t)(q_row < p.S ? q_row : 0)) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_o + c * 32, r);
+                tmem_ld_wait();
+                if (q_row < p.S) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 0]) * inv_l, __uint_as_float(r[8 * q4 + 1]) * inv_l);
+                        v.y = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 2]) * inv_l, __uint_as_float(r[8 * q4 + 3]) * inv_l);
+                        v.z = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 4]) * inv_l, __uint_as_float(r[8 * q4 + 5]) * inv_l);
+                        v.w = pack_half2<kBf16>(__uint_as_float(r[8 * q4 + 6]) * inv_l, __uint_as_float(r[8 * q4 + 7]) * inv_l);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    // ----------------------------------------------------------------- teardown
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        probe[2] = (unsigned long long)clock64();
+        probe[3] = global_timer_ns();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The rotating-buffer kernel (head dimension 64; it also runs with two buffers at head dimension 128).
 // kBf16: Q, K, V, P and O are bfloat16 (the reference interface's type, matrix_util.hpp:40-45) instead of fp16.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -374,14 +797,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         };
         // S(u) = Q_w K_j^T into score buffer u % kBufs.  (Not split along the keys: with both operands
         // in shared memory a 128 x 64 x 16 step reads 6 KB in 32 cycles, more than shared memory delivers.)
+        // (The K tile must have been waited for, and a tcgen05 fence passed, before this is called: the main
+        // loop does both before it waits for P, so that nothing stands between the P V issue and this one.
+        // A wait and a fence in between cost 3.6 % at head dimension 128.)
         auto issue_qk = [&](int u) {
             int j, w;
             use_block(u, j, w);
-            uint32_t st;
-            if (!wait_kv(2 * j, st)) {
-                return false;
-            }
-            tcgen05_fence_after();
+            const uint32_t st = (uint32_t)((2 * j) % kKvStages);
             const uint32_t buf = (uint32_t)(u % kBufs);
             const uint32_t k_lo = desc_lo_kmajor(kv_smem + st * Cfg::kTileBytes);
             const uint32_t q_lo = q_lo0 + (uint32_t)w * (Cfg::kTileBytes >> 4);
@@ -397,7 +819,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     umma_commit<1>(smem_u32(&bars->kv_empty[st]));  // the second tile is K_j's last reader
                 }
             }
-            return true;
+        };
+        // the K tile of use u has landed
+        auto wait_k = [&](int u) {
+            int j, w;
+            use_block(u, j, w);
+            uint32_t st;
+            return wait_kv(2 * j, st);
         };
         // O_w (+)= P(u) V_j: A = P in tensor memory (16 keys = 8 packed columns per step), B = the V tile
         // (N-major; its d-halves are one 128-row block apart), in two halves of 64 keys as the softmax
@@ -443,13 +871,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 break;
             }
             for (int u = 0; u < kBufs && u < n_uses && ok; ++u) {
-                ok = issue_qk(u);
+                ok = wait_k(u);
+                if (ok) {
+                    tcgen05_fence_after();
+                    issue_qk(u);
+                }
             }
             // P(u) V, then the score tile that takes over the buffer this multiply frees
             for (int u = 0; u < n_uses && ok; ++u) {
+                const bool next_qk = u + kBufs < n_uses;
+                // the tiles these multiplies read were requested long ago; make sure of them now, while the
+                // softmax is still at work
+                if (next_qk && !wait_k(u + kBufs)) {
+                    ok = false;
+                    break;
+                }
                 ok = issue_pv(u);
-                if (ok && u + kBufs < n_uses) {
-                    ok = issue_qk(u + kBufs);
+                if (ok && next_qk) {
+                    issue_qk(u + kBufs);
                 }
             }
         } while (false);
@@ -683,12 +1122,23 @@ static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int 
     return r == CUDA_SUCCESS ? 0 : SPORK_ERR_DRIVER;
 }
 
+// Head dimension 128 runs the two-buffer kernel, head dimension 64 the rotating-buffer kernel (only the
+// pairs in use are instantiated).
+template <int D, bool kBf16>
+struct KernelFor {
+    static auto get() { return attn_fwd_kernel<D, kBf16>; }
+};
+template <bool kBf16>
+struct KernelFor<128, kBf16> {
+    static auto get() { return attn_fwd_two_kernel<128, kBf16>; }
+};
+
 template <int D, bool kBf16>
 static int launch(int BH, int S, const void* q, const void* k, const void* v, void* o, float scale, bool causal,
                   DeviceState& dev, cudaStream_t stream)
 {
     using Cfg = Config<D>;
-    auto kernel = attn_fwd_kernel<D, kBf16>;
+    auto kernel = KernelFor<D, kBf16>::get();
     static std::once_flag attr_once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(attr_once[dev.ordinal], [&] {

@@ -853,10 +853,73 @@ static bool want_wide_tiles(uint32_t M, uint32_t N, uint32_t K, int max_ctas, in
     const uint64_t tiles_n = (N + kWideN - 1) / kWideN;
     const uint64_t tiles = (uint64_t)((M + 255) / 256) * tiles_n;
     const uint64_t padded_n = tiles_n * kWideN;
+    // The coarser tiles must not cost a wave: 15360 x 1536 x 8192 is 180 wide tiles = 2.4 waves of 74 pairs
+    // (three waves, 81 % of the machine-time used) but 360 narrow ones = 4.9 waves (97 %).  Compare the
+    // work in units of narrow tiles per wave slot and allow the wide tile a 2 % worse fill.
+    if (groups > 0) {
+        const uint64_t narrow_tiles = (uint64_t)((M + 255) / 256) * ((N + 255) / 256);
+        const uint64_t wide_slots = (tiles + groups - 1) / groups * groups * 2;         // in narrow-tile units
+        const uint64_t narrow_slots = (narrow_tiles + groups - 1) / groups * groups;
+        if (wide_slots * 100 > narrow_slots * 102) {
+            return false;
+        }
+    }
     // K: the tile ends cost about 5000 cycles of tensor-pipe idle time (the epilogue cannot hide behind a
     // second accumulator), against 1024 cycles per K block; measured at the power limit the wide tile wins
     // from K = 4096 upwards (8192^3 +6 %, 40016 x 32768 x 6400 +3 %) and loses below (8192 x 8192 x 2048 -6 %).
     return groups > 0 && tiles >= 2ull * groups && K >= 4096 && (padded_n - N) * 16 <= N;
+}
+
+// What a launch resolves to: tile width (512 = the 256 x 512 kernel), CTAs per tile, 128-byte column
+// blocks per ring stage, K split (-1 = stream-K).  Pure arithmetic over the arguments, the SM count and
+// the tuning knobs; shared by the launch path and spork_gemm_sm100_choice.
+struct TileChoice {
+    int block_n, cta_group, k_atoms, split_k;
+};
+
+static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k,
+                        int max_ctas, int sm_count, bool tf32, uint32_t batches)
+{
+    const bool tile_left_to_library = cta_group == 0;
+    if (block_n == kWideN) {
+        // 256 x 512 tiles on request: CTA pairs only, one matrix, output-stationary or split-K
+        if ((cta_group != 0 && cta_group != 2) || batches != 1 || split_k < 0) {
+            return false;
+        }
+        c = TileChoice{kWideN, 2, 1, split_k == 0 ? 1 : split_k};
+        return true;
+    }
+    if (cta_group == 0) {
+        // The caller left the tile to the library.  A problem that fills a small part of one wave and
+        // has a short K is bound by latencies, not by throughput: a single CTA per tile starts 1.5-2 us
+        // sooner than a pair (no cluster to form) and 128-wide tiles spread the work over more SMs
+        // (160 x 480 x 816: 9.2 us against 12.4 us; 768 x 768 x 32: 6.6 against 8.9).
+        cta_group = SPORK_DEFAULT_CTA_GROUP;
+        const uint64_t pair_tiles =
+            (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
+        if (!tf32 && split_k == 1 && K <= 1024 && pair_tiles * 4 <= (uint64_t)sm_count) {
+            cta_group = 1;
+            block_n = block_n > 128 ? 128 : block_n;
+        }
+    }
+    if (split_k == 0) {
+        split_k = (int)choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n, (uint32_t)cta_group,
+                                    tf32 ? 32u : 64u, max_ctas, sm_count, batches);
+    }
+    if (tile_left_to_library && cta_group == 2 && block_n == 256 && batches == 1 && split_k == 1 &&
+        want_wide_tiles(M, N, K, max_ctas, sm_count)) {
+        c = TileChoice{kWideN, 2, 1, 1};
+        return true;
+    }
+    // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
+    // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.
+    const uint64_t out_tiles =
+        (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
+    const bool wide_k = !tf32 && (g_tuning.k_atoms == 2 ||
+                                  (cta_group == 2 && g_tuning.k_atoms == 0 && block_n <= 128 &&
+                                   out_tiles <= (uint64_t)sm_count / 2 && K >= 2048));
+    c = TileChoice{block_n, cta_group, wide_k ? 2 : 1, split_k};
+    return true;
 }
 
 static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C, int block_n,
@@ -894,47 +957,19 @@ static int dispatch(uint32_t M, uint32_t N, uint32_t K, const void* A, const voi
     if (rc) {
         return rc;
     }
-    const bool tile_left_to_library = cta_group == 0;
-    if (block_n == kWideN) {
-        // 256 x 512 tiles on request: CTA pairs only, one matrix, output-stationary or split-K
-        if ((cta_group != 0 && cta_group != 2) || batches != 1 || split_k < 0) {
-            return SPORK_ERR_BAD_ARGUMENT;
-        }
-        const uint32_t sk = split_k == 0 ? 1u : (uint32_t)split_k;
+    TileChoice choice;
+    if (!choose_tile(choice, M, N, K, block_n, cta_group, split_k, max_ctas, dev->sm_count, tf32, batches)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    block_n = choice.block_n;
+    cta_group = choice.cta_group;
+    const bool stream_k = choice.split_k == -1;
+    const uint32_t sk = stream_k ? 1u : (uint32_t)choice.split_k;
+    if (choice.block_n == kWideN) {
         return tf32 ? launch_wide<true>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, split_inner)
                     : launch_wide<false>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, split_inner);
     }
-    if (cta_group == 0) {
-        // The caller left the tile to the library.  A problem that fills a small part of one wave and
-        // has a short K is bound by latencies, not by throughput: a single CTA per tile starts 1.5-2 us
-        // sooner than a pair (no cluster to form) and 128-wide tiles spread the work over more SMs
-        // (160 x 480 x 816: 9.2 us against 12.4 us; 768 x 768 x 32: 6.6 against 8.9).
-        cta_group = SPORK_DEFAULT_CTA_GROUP;
-        const uint64_t pair_tiles =
-            (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
-        if (!tf32 && split_k == 1 && K <= 1024 && pair_tiles * 4 <= (uint64_t)dev->sm_count) {
-            cta_group = 1;
-            block_n = block_n > 128 ? 128 : block_n;
-        }
-    }
-    if (split_k == 0) {
-        split_k = (int)choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n, (uint32_t)cta_group,
-                                    tf32 ? 32u : 64u, max_ctas, dev->sm_count, batches);
-    }
-    const bool stream_k = split_k == -1;
-    const uint32_t sk = stream_k ? 1u : (uint32_t)split_k;
-    if (tile_left_to_library && cta_group == 2 && block_n == 256 && batches == 1 && sk == 1 && !stream_k &&
-        want_wide_tiles(M, N, K, max_ctas, dev->sm_count)) {
-        return tf32 ? launch_wide<true>(M, N, K, A, B, C, 1, max_ctas, *dev, stream)
-                    : launch_wide<false>(M, N, K, A, B, C, 1, max_ctas, *dev, stream);
-    }
-    // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
-    // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.
-    const uint64_t out_tiles =
-        (uint64_t)((M + 255) / 256) * ((N + (uint32_t)block_n - 1) / (uint32_t)block_n) * batches;
-    const bool wide_k = !tf32 && (g_tuning.k_atoms == 2 ||
-                                  (cta_group == 2 && g_tuning.k_atoms == 0 && block_n <= 128 &&
-                                   out_tiles <= (uint64_t)dev->sm_count / 2 && K >= 2048));
+    const bool wide_k = choice.k_atoms == 2;
     if (!tf32 && g_tuning.k_atoms == 3 && cta_group == 2 && block_n <= 128) {
         // four column blocks (512 contiguous bytes per row and request): an experiment for the skinny shapes
         return block_n == 64 ? launch<2, 64, false, 4>(M, N, K, A, B, C, sk, max_ctas, *dev, stream, stream_k, batches, split_inner)
@@ -1327,6 +1362,28 @@ extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int 
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;
     spork::gemm_sm100::g_tuning.l2_hints = l2_hints;
     spork::gemm_sm100::g_tuning.backoff_ns = backoff_ns;
+    return 0;
+}
+
+extern "C" int spork_gemm_sm100_choice(uint32_t M, uint32_t N, uint32_t K, int variant, int split_k, int sm_count, int tf32,
+                                       int* out)
+{
+    int block_n = variant;
+    if (variant == 0) {
+        block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
+    }
+    if (!out || sm_count < 2 || (block_n != 64 && block_n != 128 && block_n != 256 && block_n != 512)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::gemm_sm100::TileChoice c;
+    if (!spork::gemm_sm100::choose_tile(c, M, N, K, block_n, variant == 0 ? 0 : SPORK_DEFAULT_CTA_GROUP, split_k, 0,
+                                        sm_count, tf32 != 0, 1)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    out[0] = c.block_n;
+    out[1] = c.cta_group;
+    out[2] = c.k_atoms;
+    out[3] = c.split_k;
     return 0;
 }
 

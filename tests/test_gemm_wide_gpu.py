@@ -88,7 +88,7 @@ def test_library_choice_equals_the_narrow_kernel(sp, orc, cuda):
     result is the same bits."""
     import torch
 
-    M, N, K = 4864, 8192, 4096  # 19 x 16 = 304 wide tiles: more than two waves of 74 pairs, and a long K
+    M, N, K = 9472, 8192, 4096  # 37 x 16 = 592 wide tiles: eight full waves of 74 pairs, and a long K
     a, b = _inputs(sp, orc, cuda, M, N, K)
     outs = []
     for wide in (0, 1, 2):
@@ -103,7 +103,7 @@ def test_library_choice_equals_the_narrow_kernel(sp, orc, cuda):
         outs.append(c)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
     A, B = a.cpu().numpy(), b.cpu().numpy()
-    for m0 in (0, 2400, M - 16):
+    for m0 in (0, 4800, M - 16):
         ref = orc.gemm_f16f32_rows(A, B, m0, 16)
         assert orc.normalised_error(outs[0][m0:m0 + 16].cpu().numpy(), ref, 1.0, 1.0, K) < 1e-2
 

@@ -123,3 +123,31 @@ def test_automatic_split_fills_the_waves(L):
                 assert (m, n, kb) not in seen
                 seen[(m, n, kb)] = True
     assert len(seen) == p["tiles_m"] * p["tiles_n"] * p["num_kb"]
+
+
+def test_tile_choice_of_the_default_entry_point(sp):
+    """What a launch resolves to, without a GPU: width from N for skinny problems (two column blocks per stage
+    when K is long), single CTAs for tiny latency-bound ones, 256 x 512 pair tiles for large deep problems whose
+    waves they fill as well as 256 x 256 tiles do."""
+    c = sp.choice
+    assert c(8192, 8192, 8192) == {"block_n": 512, "cta_group": 2, "k_atoms": 1, "split_k": 1}
+    assert c(65536, 8192, 8192)["block_n"] == 512 and c(40016, 32768, 6400)["block_n"] == 512
+    assert c(8192, 8192, 2048)["block_n"] == 256          # short K: the tile ends would cost more than the bytes save
+    assert c(4096, 4096, 4096)["block_n"] == 256          # 128 wide tiles: less than two waves
+    assert c(15360, 1536, 8192)["block_n"] == 256         # 180 wide tiles = 2.4 waves (three), 360 narrow = 4.9 (five)
+    assert c(7680, 3072, 16384)["block_n"] == 256
+    assert c(8192, 8200, 8192)["block_n"] == 256          # 8200 columns would pad the last tile column to 8704
+    for n in (64, 128):
+        assert c(16384, n, 8192) == {"block_n": n, "cta_group": 2, "k_atoms": 2, "split_k": 1}
+    assert c(16384, 256, 8192) == {"block_n": 256, "cta_group": 2, "k_atoms": 1, "split_k": 1}
+    assert c(160, 480, 816) == {"block_n": 128, "cta_group": 1, "k_atoms": 1, "split_k": 1}
+    assert c(256, 256, 512)["cta_group"] == 1
+    assert c(8192, 8192, 8192, variant=256)["block_n"] == 256 and c(512, 512, 512, variant=512)["block_n"] == 512
+    assert c(1536, 2304, 65536, variant=256, split_k=0)["split_k"] == 4      # the automatic K split
+    assert c(8192, 8192, 8192, tf32=True)["block_n"] == 512
+    assert c(8192, 8192, 8192, sm_count=132)["block_n"] in (256, 512)        # another SM count: still a valid answer
+    try:
+        sp.tune(wide=1)
+        assert c(8192, 8192, 8192)["block_n"] == 256
+    finally:
+        sp.tune()
