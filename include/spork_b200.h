@@ -154,7 +154,9 @@ int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz);
  * stream-ordered kernels instead of programmatic dependents (by default a launch
  * sets up its barriers and tensor memory while the previous kernel in the stream
  * is still finishing on other SMs, and waits for it before touching global
- * memory).  spork_gemm_sm100_tuning reads
+ * memory); bit 25: problems that underfill the machine keep 256-wide tiles (by
+ * default variant 0 narrows the tile to 128 or 64 columns when that fills the
+ * waves better).  spork_gemm_sm100_tuning reads
  * the knobs back.  The reference
  * fixes the equivalent choices at compile time (gemm/gemm_sm90.cu:1278-1289). */
 int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns);

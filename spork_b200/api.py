@@ -247,12 +247,13 @@ def last_clock_mhz(stream=None) -> float:
 
 def tune(stages: int = 0, group_m: int = 0, l2_hints: int = 0, backoff_ns: int = 0, *, experiment: int = 0,
          k_atoms: int = 0, wide: int = 0, wide_skew: int = 0, wide_group_m: int = 0,
-         no_early_launch: bool = False) -> None:
+         no_early_launch: bool = False, keep_wide_tiles: bool = False) -> None:
     """Process-wide tuning knobs of later GEMM launches (see spork_gemm_sm100_tune in the header).
 
     ``l2_hints`` may carry the packed upper bits itself (the C form); the keyword arguments are OR-ed in."""
     packed = l2_hints | ((experiment & 15) << 4) | ((k_atoms & 3) << 8) | ((wide & 3) << 10) | \
-        ((wide_skew & 15) << 12) | ((wide_group_m & 255) << 16) | (int(bool(no_early_launch)) << 24)
+        ((wide_skew & 15) << 12) | ((wide_group_m & 255) << 16) | (int(bool(no_early_launch)) << 24) | \
+        (int(bool(keep_wide_tiles)) << 25)
     _check(lib().spork_gemm_sm100_tune(stages, group_m, packed, backoff_ns), "spork_gemm_sm100_tune")
 
 

@@ -642,6 +642,7 @@ struct Tuning {
     int wide_skew = 0;    // 0 = default (ring depth)
     int wide_group_m = 0; // 0 = default raster group of the 256 x 512 kernel
     int no_early_launch = 0;  // 1: launches are not programmatic dependents (no overlap with the previous kernel's tail)
+    int narrow = 0;           // 1: problems that underfill the machine keep 256-wide tiles (no 128- / 64-wide choice)
     unsigned long long* trace = nullptr;  // spork_gemm_sm100_trace
     uint32_t trace_items = 0;
 };
@@ -905,6 +906,33 @@ static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int b
     if (split_k == 0) {
         split_k = (int)choose_split(M, N, K, 128u * (uint32_t)cta_group, (uint32_t)block_n, (uint32_t)cta_group,
                                     tf32 ? 32u : 64u, max_ctas, sm_count, batches);
+    }
+    if (tile_left_to_library && cta_group == 2 && block_n == 256 && split_k == 1 && g_tuning.narrow != 1) {
+        // A problem with fewer 256-wide tiles than CTA pairs leaves SMs idle; 128- or 64-wide tiles fill the
+        // machine instead (768 x 3072 x 3072: 36 tiles of 256 columns, 72 of 128).  Modelled time = waves x
+        // (K blocks x cycles per K block + a tile's fixed cost); cycles per K block 550 / 410 / 340 for 256 /
+        // 128 / 64 columns: narrower tiles pull more operand bytes per FLOP through L2 (32 / 24 / 20 KB per CTA
+        // and K block), and about 60 bytes per clock and SM is what L2 delivers when every SM asks (measured:
+        // 2304 x 2816 x 65536 runs 565 cycles per K block with 256-wide and 420 with 128-wide tiles).  The
+        // narrower tile must win by 15 %.
+        uint32_t groups = (uint32_t)sm_count / 2u;
+        if (max_ctas > 0 && (uint32_t)max_ctas / 2u < groups) {
+            groups = (uint32_t)max_ctas / 2u;
+        }
+        if (groups > 0) {
+            const uint64_t num_kb = (K + (tf32 ? 32u : 64u) - 1) / (tf32 ? 32u : 64u);
+            const uint64_t tiles_m = (uint64_t)((M + 255) / 256) * batches;
+            auto cost = [&](uint32_t bn, uint64_t cycles_per_kb) {
+                const uint64_t tiles = tiles_m * ((N + bn - 1) / bn);
+                return ((tiles + groups - 1) / groups) * (num_kb * cycles_per_kb + 3000);
+            };
+            const uint64_t c256 = cost(256, 550), c128 = cost(128, 410), c64 = cost(64, 340);
+            if (c128 * 100 < c256 * 85 && c128 <= c64) {
+                block_n = 128;
+            } else if (c64 * 100 < c256 * 85 && c64 < c128) {
+                block_n = 64;
+            }
+        }
     }
     if (tile_left_to_library && cta_group == 2 && block_n == 256 && batches == 1 && split_k == 1 &&
         want_wide_tiles(M, N, K, max_ctas, sm_count)) {
@@ -1347,7 +1375,7 @@ extern "C" int spork_gemm_sm100_last_clock_mhz(void* stream, double* mhz)
 
 extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int backoff_ns)
 {
-    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x1FFFFFF || 
+    if (stages < 0 || group_m < 0 || l2_hints < 0 || l2_hints > 0x3FFFFFF || 
         ((l2_hints >> 10) & 3) > 2 || backoff_ns < 0 || backoff_ns > 100000) {
         return SPORK_ERR_BAD_ARGUMENT;
     }
@@ -1357,6 +1385,7 @@ extern "C" int spork_gemm_sm100_tune(int stages, int group_m, int l2_hints, int 
     spork::gemm_sm100::g_tuning.wide_skew = (l2_hints >> 12) & 15; // bits 12..15: their skew, 0 = default
     spork::gemm_sm100::g_tuning.wide_group_m = (l2_hints >> 16) & 255;  // bits 16..23: their raster group, 0 = default
     spork::gemm_sm100::g_tuning.no_early_launch = (l2_hints >> 24) & 1; // bit 24: plain stream order, no early set-up
+    spork::gemm_sm100::g_tuning.narrow = (l2_hints >> 25) & 1;          // bit 25: never narrow the tile to fill the machine
     l2_hints &= 15;   // bit 3 = "no hints at all" must survive (see effective_l2_hints)
     spork::gemm_sm100::g_tuning.stages = stages;
     spork::gemm_sm100::g_tuning.group_m = group_m == 0 ? spork::gemm_sm100::kGroupM : group_m;

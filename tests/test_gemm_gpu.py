@@ -455,3 +455,22 @@ def test_tensor_maps_are_encoded_once_per_operand(sp, orc, cuda):
     assert m2 - m1 == 3
     sp.status()
     _check(sp, orc, a2, b2, c2, 1024)
+
+
+@pytest.mark.parametrize("shape", [(768, 3072, 3072), (1536, 768, 4096), (768, 2816, 4096)])
+def test_default_entry_narrows_the_tile_to_fill_the_machine(sp, orc, cuda, shape):
+    """Problems with fewer 256-wide tiles than CTA pairs run with 128- or 64-wide tiles through the default
+    entry point; same result as the 256-wide tile taken literally (same order of accumulation per element)."""
+    import torch
+
+    M, N, K = shape
+    assert sp.choice(M, N, K)["block_n"] in (64, 128)
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c)
+    sp.status()
+    _check(sp, orc, a, b, c, K)
+    wide = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, wide, variant=256)
+    sp.status()
+    assert torch.equal(c, wide)

@@ -151,3 +151,19 @@ def test_tile_choice_of_the_default_entry_point(sp):
         assert c(8192, 8192, 8192)["block_n"] == 256
     finally:
         sp.tune()
+
+
+def test_tile_narrows_when_256_wide_tiles_underfill_the_machine(sp):
+    c = sp.choice
+    assert c(768, 3072, 3072)["block_n"] == 128        # 36 tiles of 256 columns for 74 CTA pairs; 72 of 128
+    assert c(1536, 768, 65536)["block_n"] == 64        # 18 -> 72 tiles
+    assert c(768, 2816, 65536)["block_n"] == 128       # 33 -> 66 tiles, still one wave
+    assert c(2304, 2816, 65536)["block_n"] == 256      # 99 tiles = two waves; 198 narrower ones = three waves that
+                                                       # are not short enough (narrow tiles are bound by L2)
+    assert c(2048, 2048, 2048)["block_n"] == 256       # 64 tiles: narrower tiles would need a second wave
+    assert c(12288, 24576, 1536)["block_n"] == 256     # many waves: nothing to gain
+    try:
+        sp.tune(keep_wide_tiles=True)
+        assert c(768, 3072, 3072)["block_n"] == 256
+    finally:
+        sp.tune()
