@@ -229,14 +229,14 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
 
 // ---------------------------------------------------------------------------------------------------
 // The two-buffer kernel (head dimension 128): score buffer w belongs to query tile w, S_w(j+1) is issued
-// after P_w(j) V_j has consumed the buffer, both tiles walk the same key blocks (with a causal mask the
-// first tile sees its last block fully masked).  It is kept as a kernel of its own, apart from the
+// after P_w(j) V_j has consumed the buffer.  kCausal: compiled with the mask, each tile stopping at its own
+// diagonal block (the non-causal instance carries none of that code).  It is kept as a kernel of its own, apart from the
 // rotating-buffer kernel below that head dimension 64 uses: with everything about a tile a compile-time
 // offset its MMA issuer is a few instructions per multiply, and measured on the same box it is 4-7 %
 // faster at head dimension 128 than the general kernel run with two buffers (the kernel is sensitive to
 // the issuer's instruction count and to instruction-cache pressure on the issuer's sub-partition).
 // kBf16: Q, K, V, P and O are bfloat16 (the reference interface's type, matrix_util.hpp:40-45) instead of fp16.
-template <int D, bool kBf16>
+template <int D, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kNumThreads, 1)
 attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const Params p)
@@ -264,12 +264,14 @@ attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     const int head = blockIdx.x / p.q_pairs;
     // causal: the pairs with the most key blocks are launched first, so the short ones fill the tail
-    const int q_pair = p.causal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
+    const int q_pair = kCausal ? p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs) : (int)(blockIdx.x % p.q_pairs);
     const int q_row0 = q_pair * 2 * kTileQ;
-    // causal: keys beyond this CTA's last query row are never needed (both tiles walk the same blocks; the
-    // first tile sees its last block fully masked)
+    // causal: keys beyond a tile's last query row are never needed, so the first tile stops one block
+    // before the second (n_blocks0 = n_blocks - 1, or the same when the second tile lies past the end)
     const int last_row = q_row0 + 2 * kTileQ - 1 < p.S - 1 ? q_row0 + 2 * kTileQ - 1 : p.S - 1;
-    const int n_blocks = p.causal ? last_row / kTileKV + 1 : p.kv_blocks;
+    const int last_row0 = q_row0 + kTileQ - 1 < p.S - 1 ? q_row0 + kTileQ - 1 : p.S - 1;
+    const int n_blocks = kCausal ? last_row / kTileKV + 1 : p.kv_blocks;
+    const int n_blocks0 = kCausal ? last_row0 / kTileKV + 1 : n_blocks;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
@@ -437,6 +439,10 @@ attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     if (!ok) {
                         break;
                     }
+                    if (kCausal && w == 0 && j >= n_blocks0) {
+                        continue;  // the first tile is past its diagonal
+                    }
+                    const bool more_w = (kCausal && w == 0) ? j + 1 < n_blocks0 : more;
                     if (!wait(&bars->p_ready[w][0], (uint32_t)(j & 1), 0x30 + w)) {
                         ok = false;
                         break;
@@ -449,7 +455,7 @@ attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     }
                     tcgen05_fence_after();
                     issue_pv(w, v_stage, true, 1);
-                    if (more) {
+                    if (more_w) {
                         issue_qk(w, k_stage);
                     } else {
                         commit(&bars->pv_done[w]);  // completes once: O_w is final
@@ -477,7 +483,8 @@ attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         float m_ref = -INFINITY;  // row max the stored O and l are relative to (raw scores)
         float l_run = 0.0f;       // running row sum
         bool ok = true;
-        for (int j = 0; j < n_blocks; ++j) {
+        const int n_blocks_w = w == 0 ? n_blocks0 : n_blocks;
+        for (int j = 0; j < n_blocks_w; ++j) {
             if (!mbar_wait(smem_u32(&bars->s_full[w]), (uint32_t)(j & 1), abort_flag, kSoftmaxBackoffNs)) {
                 if (lane == 0) {
                     report_timeout(p, abort_flag, 3, 0x10 + w);
@@ -502,7 +509,7 @@ attn_fwd_two_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             int valid = p.S - j * kTileKV;  // keys of this block that exist
             bool masked = valid < kTileKV;  // uniform over the CTA
-            if (p.causal) {
+            if (kCausal) {
                 // keys of this block this row may see: global key index <= global query index
                 const int row_global = q_row0 + (int)w * kTileQ + (int)row;
                 const int seen = row_global - j * kTileKV + 1;
@@ -1126,11 +1133,14 @@ static int make_tmap_bsd(CUtensorMap* map, const void* base, int BH, int S, int 
 // pairs in use are instantiated).
 template <int D, bool kBf16>
 struct KernelFor {
-    static auto get() { return attn_fwd_kernel<D, kBf16>; }
+    static auto get(bool) { return attn_fwd_kernel<D, kBf16>; }
 };
 template <bool kBf16>
 struct KernelFor<128, kBf16> {
-    static auto get() { return attn_fwd_two_kernel<128, kBf16>; }
+    static auto get(bool causal)
+    {
+        return causal ? attn_fwd_two_kernel<128, kBf16, true> : attn_fwd_two_kernel<128, kBf16, false>;
+    }
 };
 
 template <int D, bool kBf16>
@@ -1138,12 +1148,16 @@ static int launch(int BH, int S, const void* q, const void* k, const void* v, vo
                   DeviceState& dev, cudaStream_t stream)
 {
     using Cfg = Config<D>;
-    auto kernel = KernelFor<D, kBf16>::get();
+    auto kernel = KernelFor<D, kBf16>::get(causal);
     static std::once_flag attr_once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(attr_once[dev.ordinal], [&] {
-        attr_err[dev.ordinal] =
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        attr_err[dev.ordinal] = cudaFuncSetAttribute(KernelFor<D, kBf16>::get(false),
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (attr_err[dev.ordinal] == cudaSuccess) {
+            attr_err[dev.ordinal] = cudaFuncSetAttribute(
+                KernelFor<D, kBf16>::get(true), cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        }
     });
     if (attr_err[dev.ordinal] != cudaSuccess) {
         return (int)attr_err[dev.ordinal];

@@ -28,10 +28,15 @@ struct Params {
     uint32_t group_m;            // raster: m-tiles per group
     uint32_t l2_hints;           // bit 0: A loads evict_last, bit 1: B loads evict_last, bit 2: B loads evict_first
     uint32_t backoff_ns;         // sleep between polls of the long (epilogue / producer) waits; 0 = spin
-    // stream-K: the last `sk_tiles` tiles (raster order) are cut along K into one contiguous share of
-    // K blocks per CTA group and reduce-added into a zeroed C; the first `dp_tiles` run whole.
+    // stream-K: the first `dp_tiles` tiles of the raster (whole waves) run tile by tile; each of the last
+    // `sk_tiles` (fewer than there are CTA groups) is cut along K into `sk_extra` ranges of `sk_share` K
+    // blocks, one (tile, range) per CTA group, all groups running theirs at the same time over the same K
+    // offsets (so concurrent CTAs still share operand strips in L2), and reduce-added into C, which the
+    // kernel itself zeroes there at its start.
     uint32_t dp_tiles, sk_tiles;
-    uint32_t sk_share, sk_extra; // group g owns sk_share (+1 if g < sk_extra) K blocks of the stream-K part
+    uint32_t sk_share, sk_extra; // K blocks per range, ranges per tile
+    uint32_t* sk_counter;        // counts the warps that have finished zeroing their share of the stream-K tiles
+    uint32_t sk_target;          // value of *sk_counter (modulo 2^32) from which every share is zeroed
     uint32_t wide_skew;          // 256 x 512 tiles: K blocks of one accumulator half issued ahead of the other at both
                                  // ends of a tile (1 .. ring depth)
     uint32_t experiment;         // diagnostics: bit 3 (256 x 512 kernel, results unchanged) = plain stores instead of TMA
@@ -69,8 +74,7 @@ SPORK_HD void decode_tile(const Params& p, uint32_t t, WorkItem& w)
 }
 
 // Work of CTA group `g` of `G`.  Without stream-K: items g, g+G, ... of the (split, tile) list.  With
-// stream-K: first the whole tiles g, g+G, ... < dp_tiles, then this group's share of the K blocks of the
-// remaining tiles, which touches one or a few consecutive tiles.
+// stream-K: first the whole tiles g, g+G, ... < dp_tiles, then at most one K range of one of the remaining tiles.
 SPORK_HD uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
 {
     if (p.sk_tiles == 0) {
@@ -78,12 +82,7 @@ SPORK_HD uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
         return items > g ? (items - g - 1) / G + 1 : 0;
     }
     const uint32_t n1 = p.dp_tiles / G;  // dp_tiles is a multiple of G
-    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-    if (cnt == 0) {
-        return n1;
-    }
-    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-    return n1 + ((u0 + cnt - 1) / p.num_kb - u0 / p.num_kb + 1);
+    return n1 + (g < p.sk_tiles * p.sk_extra ? 1u : 0u);
 }
 
 SPORK_HD WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i)
@@ -116,14 +115,12 @@ SPORK_HD WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i
         w.reduce = false;
         return w;
     }
-    const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-    const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-    const uint32_t rel = u0 / p.num_kb + (i - n1);   // tile index inside the stream-K part
-    const uint32_t t0 = rel * p.num_kb;              // its first K-block unit
-    decode_tile(p, p.dp_tiles + rel, w);
-    w.kb_begin = u0 > t0 ? u0 - t0 : 0;
-    const uint32_t u1 = u0 + cnt;
-    w.kb_end = u1 < t0 + p.num_kb ? u1 - t0 : p.num_kb;
+    // the group's one stream-K item: ranges of one tile sit sk_tiles groups apart
+    w.split = g / p.sk_tiles;
+    decode_tile(p, p.dp_tiles + g % p.sk_tiles, w);
+    w.kb_begin = w.split * p.sk_share;
+    const uint32_t e = w.kb_begin + p.sk_share;
+    w.kb_end = e < p.num_kb ? e : p.num_kb;
     w.reduce = true;
     return w;
 }
@@ -216,13 +213,24 @@ inline void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uin
         groups = 1;
     }
     const uint32_t tiles = p.tiles_m * p.tiles_n;
-    if (stream_k && p.split_k == 1 && tiles % groups != 0) {
-        // whole waves run tile by tile; the K blocks of the last partial wave are dealt out evenly
-        p.dp_tiles = tiles / groups * groups;
-        p.sk_tiles = tiles - p.dp_tiles;
-        const uint64_t units = (uint64_t)p.sk_tiles * p.num_kb;
-        p.sk_share = (uint32_t)(units / groups);
-        p.sk_extra = (uint32_t)(units % groups);
+    const uint32_t tail = tiles % groups;
+    // ranges per tail tile: as many as there are groups to run them at once, each at least 4 K blocks long
+    uint32_t ranges = tail ? groups / tail : 1;
+    uint32_t kb_per_range = p.num_kb;
+    if (ranges > 1) {
+        kb_per_range = (p.num_kb + ranges - 1) / ranges;
+        kb_per_range = kb_per_range < 4 ? 4 : kb_per_range;
+        ranges = (p.num_kb + kb_per_range - 1) / kb_per_range;  // no empty ranges
+    }
+    if (stream_k && p.split_k == 1 && ranges > 1) {
+        // whole waves run tile by tile; the tiles of the last partial wave are cut into aligned K ranges
+        p.dp_tiles = tiles - tail;
+        p.sk_tiles = tail;
+        p.sk_share = kb_per_range;
+        p.sk_extra = ranges;
+        if (p.dp_tiles == 0) {
+            groups = tail * ranges;
+        }
     } else if (items < groups) {
         groups = (uint32_t)items;
     }
