@@ -70,21 +70,29 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
  *   block_n   64 / 128 / 256   output-tile width
  *   cta_group 1 = one CTA per tile (128 x block_n),
  *             2 = a CTA pair per tile (256 x block_n, tcgen05 cta_group::2)
- *   split_k   0: chosen by the library (1 unless the problem has fewer 256-wide
- *             output tiles than CTA pairs and a long K; then the count that
- *             fills the waves best, see spork_gemm_sm100_plan);
+ *   split_k   0: chosen by the library: 1, or, for a problem with fewer 256-wide
+ *             output tiles than CTA pairs and a long K, the count that fills
+ *             the waves best, or stream-K (-1) when the last of several waves
+ *             of tiles is less than half full (see spork_gemm_sm100_plan and
+ *             spork_gemm_sm100_choice);
  *             >= 1: K is cut into split_k ranges whose partial products are
  *             added into C with TMA reduce-add (C is zeroed first); the
  *             counterpart of gemm_sm90_k_mode::split_k_outer
  *             (gemm/gemm_sm90.h:8, gemm/gemm_sm90.cu:1096-1114).
  *             -1: stream-K, the counterpart of gemm_sm90_k_mode::stream_k_*
  *             (gemm/gemm_sm90.h:10-11, gemm/gemm_sm90.cu:1004-1094): whole
- *             waves of tiles run one tile per CTA pair, the K blocks of the
- *             last partial wave are dealt out evenly over all CTA pairs and
- *             reduce-added into their (zeroed) tiles.  A compatibility mode:
- *             CTA pairs that share a tile sit at different K offsets, so
- *             concurrent tiles no longer sweep shared strips of A and B through
- *             L2 together, and split_k = 0 is faster on every shape measured.
+ *             waves of tiles run one tile per CTA pair; each tile of the last
+ *             partial wave, when that wave is at most half full, is cut into
+ *             as many equal K ranges as there are CTA pairs to run them at the
+ *             same time, all tiles at the same K offsets (so concurrent pairs
+ *             still sweep shared strips of A and B through L2), and the ranges
+ *             are reduce-added into C.  The kernel zeroes those tiles itself
+ *             while its epilogue warps wait for the first tile, and its CTAs
+ *             meet at a device counter before the first reduce-add (a bounded
+ *             wait): the launch relies on all its CTAs being resident
+ *             together, which holds when it has the device to itself, so do
+ *             not run stream-K launches of several streams at the same time.
+ *             A last wave more than half full runs whole (no ranges).
  *             <= -2: |split_k| ranges like >= 2, but the ranges of one tile are
  *             neighbours in the schedule (K fastest), the counterpart of
  *             gemm_sm90_k_mode::split_k_inner (gemm/gemm_sm90.h:9).

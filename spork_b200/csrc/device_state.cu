@@ -34,13 +34,14 @@ int current_device_state(DeviceState** out)
         if (e != cudaSuccess) {
             return (int)e;
         }
-        // 64 bytes: [0] status word, [16..48) clock probe of the last GEMM launch (see gemm_sm100.cu)
+        // 256 bytes: [0] status word, [16..48) clock probe of the last GEMM launch (see gemm_sm100.cu),
+        // [128..192) the stream-K counters
         uint32_t* word = nullptr;
-        e = cudaMalloc(&word, 64);
+        e = cudaMalloc(&word, 256);
         if (e != cudaSuccess) {
             return (int)e;
         }
-        e = cudaMemset(word, 0, 64);
+        e = cudaMemset(word, 0, 256);
         if (e != cudaSuccess) {
             cudaFree(word);
             return (int)e;
@@ -52,6 +53,25 @@ int current_device_state(DeviceState** out)
     }
     *out = &s;
     return 0;
+}
+
+void reserve_sk_counter(DeviceState& dev, uint32_t arrivals, uint32_t** counter, uint32_t* target)
+{
+    std::lock_guard<std::mutex> lock(dev.sk_mutex);
+    const uint32_t slot = dev.sk_next++ % (uint32_t)DeviceState::kSkCounters;
+    dev.sk_reached[slot] += arrivals;  // modulo 2^32, like the counter itself
+    *counter = dev.status_word + DeviceState::kSkCounterWord0 + slot;
+    *target = dev.sk_reached[slot];
+}
+
+void reset_sk_counters(DeviceState& dev, cudaStream_t stream)
+{
+    std::lock_guard<std::mutex> lock(dev.sk_mutex);
+    cudaMemsetAsync(dev.status_word + DeviceState::kSkCounterWord0, 0, sizeof(uint32_t) * DeviceState::kSkCounters,
+                    stream);
+    for (int i = 0; i < DeviceState::kSkCounters; ++i) {
+        dev.sk_reached[i] = 0;
+    }
 }
 
 int ensure_staging(DeviceState& dev, int slot, size_t bytes)
@@ -120,6 +140,7 @@ extern "C" int spork_gemm_sm100_status(void* stream, uint32_t* detail)
     }
     if (word != 0) {
         cudaMemsetAsync(dev->status_word, 0, sizeof(word), s);
+        spork::reset_sk_counters(*dev, s);
         cudaStreamSynchronize(s);
         // 0xC.......: a range check of the debug build; anything else: a bounded wait that ran out
         return (word >> 28) == 0xCu ? SPORK_ERR_DEVICE_CHECK : SPORK_ERR_DEVICE_TIMEOUT;

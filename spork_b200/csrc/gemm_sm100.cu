@@ -349,8 +349,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t local = 0;
         uint32_t slab_sel = 0;
         bool ok = true;
+        bool sk_zeroed = p.sk_tiles == 0;  // the stream-K tiles are known to be zero everywhere
+        if (p.sk_tiles != 0) {
+            // Stream-K tiles are accumulated by reduce-adds, so C must be zero there first.  The epilogue
+            // warps have nothing to do until the first tile is complete: each zeroes its share of the rows
+            // (one 256-column tile row = 1 KB at a time) and counts itself in; the count is checked before
+            // this warp's first reduce-add, whole tiles later.
+            const uint32_t warps_total = gridDim.x * kNumEpilogueWarps;
+            const uint32_t rows_total = p.sk_tiles * Cfg::kUmmaM;
+            for (uint32_t r = blockIdx.x * kNumEpilogueWarps + epi; r < rows_total; r += warps_total) {
+                WorkItem z;
+                decode_tile(p, p.dp_tiles + r / Cfg::kUmmaM, z);
+                const uint32_t row = z.m_tile * Cfg::kUmmaM + r % Cfg::kUmmaM;
+                const uint32_t col0 = z.n_tile * BLOCK_N;
+                if (row >= p.M || col0 >= p.N) {
+                    continue;
+                }
+                const uint32_t cols = p.N - col0 < (uint32_t)BLOCK_N ? p.N - col0 : (uint32_t)BLOCK_N;
+                float* dst = p.C + (size_t)row * p.N + col0;
+                if (p.use_tma_store) {
+                    // N % 4 == 0 and C is 16-byte aligned: so is every tile row
+                    for (uint32_t c = lane * 4; c < cols; c += 128) {
+                        *reinterpret_cast<float4*>(dst + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                } else {
+                    for (uint32_t c = lane; c < cols; c += 32) {
+                        dst[c] = 0.0f;
+                    }
+                }
+            }
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) {
+                red_release_gpu_add(p.sk_counter, 1u);
+            }
+        }
         for (uint32_t item = 0; item < num_items && ok; ++item, ++local) {
             const WorkItem w = group_item(p, group_id, num_groups, item);
+            if (w.reduce && !sk_zeroed) {
+                if (!counter_wait(p.sk_counter, p.sk_target, abort_flag)) {
+                    if (lane == 0) {
+                        report_timeout(p, abort_flag, 3, 0x48);
+                    }
+                    ok = false;
+                    break;
+                }
+                fence_proxy_async_all();
+                sk_zeroed = true;
+            }
             const uint32_t buf = local & 1u;
             const uint32_t acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase, abort_flag, p.backoff_ns)) {
@@ -477,22 +523,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (!kWorkspace && blockIdx.x == 0 && threadIdx.x == 0) {
         probe[2] = (unsigned long long)clock64();
         probe[3] = global_timer_ns();
-    }
-}
-
-// Zeroes the output tiles that stream-K accumulates into (tiles [first_tile, first_tile + count) of the
-// raster; one block per tile).
-template <int TILE_M, int TILE_N>
-__global__ void __launch_bounds__(256) zero_tiles_kernel(const Params p, uint32_t first_tile)
-{
-    WorkItem w;
-    decode_tile(p, first_tile + blockIdx.x, w);
-    const uint32_t m0 = w.m_tile * TILE_M, n0 = w.n_tile * TILE_N;
-    for (uint32_t i = threadIdx.x; i < (uint32_t)(TILE_M * TILE_N); i += blockDim.x) {
-        const uint32_t m = m0 + i / TILE_N, n = n0 + i % TILE_N;
-        if (m < p.M && n < p.N) {
-            p.C[(size_t)m * p.N + n] = 0.0f;
-        }
     }
 }
 
@@ -727,11 +757,8 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     }
 
     if (p.sk_tiles != 0) {
-        zero_tiles_kernel<Cfg::kUmmaM, BLOCK_N><<<p.sk_tiles, 256, 0, stream>>>(p, p.dp_tiles);
-        const cudaError_t ze = cudaGetLastError();
-        if (ze != cudaSuccess) {
-            return (int)ze;
-        }
+        // the kernel zeroes the stream-K tiles itself; its CTAs meet at one of the device's counters
+        reserve_sk_counter(dev, groups * CG * kNumEpilogueWarps, &p.sk_counter, &p.sk_target);
     }
 
     cudaLaunchConfig_t cfg{};
@@ -882,6 +909,7 @@ static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int b
                         int max_ctas, int sm_count, bool tf32, uint32_t batches)
 {
     const bool tile_left_to_library = cta_group == 0;
+    const bool split_left_to_library = split_k == 0;
     if (block_n == kWideN) {
         // 256 x 512 tiles on request: CTA pairs only, one matrix, output-stationary or split-K
         if ((cta_group != 0 && cta_group != 2) || batches != 1 || split_k < 0) {
@@ -938,6 +966,23 @@ static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int b
         want_wide_tiles(M, N, K, max_ctas, sm_count)) {
         c = TileChoice{kWideN, 2, 1, 1};
         return true;
+    }
+    if (split_left_to_library && split_k == 1 && cta_group == 2 && block_n == 256 && batches == 1) {
+        // More than one wave of tiles, the last one less than half full: stream-K cuts the tiles of that
+        // wave into two or more K ranges that run at the same time (4096^3: 256 tiles = 3 waves of 74 CTA
+        // pairs + 34 tiles, each cut in two: 3.5 tile-times instead of 4).  Modelled as in the narrowing
+        // above, with a reduce-add epilogue at 6000 cycles; stream-K must win by 7 %.
+        Params sp{};
+        uint32_t sg = 0;
+        plan_launch(sp, sg, M, N, K, 256u, 256u, 2u, tf32 ? 32u : 64u, 1u, true, max_ctas, sm_count, 1);
+        if (sp.sk_tiles != 0 && sp.dp_tiles != 0) {
+            const uint64_t tile_time = (uint64_t)sp.num_kb * 550 + 3000;
+            const uint64_t t_whole = (uint64_t)(sp.dp_tiles / sg + 1) * tile_time;
+            const uint64_t t_stream = (uint64_t)(sp.dp_tiles / sg) * tile_time + (uint64_t)sp.sk_share * 550 + 6000;
+            if (t_stream * 100 < t_whole * 93) {
+                split_k = -1;
+            }
+        }
     }
     // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into
     // streaming A from HBM, and 256-byte row segments use the DRAM pages better than 128-byte ones.

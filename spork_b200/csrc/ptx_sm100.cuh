@@ -200,6 +200,47 @@ __device__ __forceinline__ void fence_proxy_async_smem()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Order generic-proxy accesses (of any state space, here: other CTAs' plain stores to global memory that an
+// acquire has made visible) before later async-proxy accesses (TMA reduce-adds) of this thread.
+__device__ __forceinline__ void fence_proxy_async_all()
+{
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Counter in global memory that CTAs of one grid signal each other through.
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* addr, uint32_t v)
+{
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* addr)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// Bounded wait until the counter has reached `target` (modulo 2^32).  Returns false if abandoned.
+__device__ __forceinline__ bool counter_wait(const uint32_t* addr, uint32_t target, volatile uint32_t* abort_flag,
+                                             uint64_t limit_ns = kWaitLimitNs)
+{
+    if ((int32_t)(ld_acquire_gpu(addr) - target) >= 0) {
+        return true;
+    }
+    const uint64_t deadline = global_timer_ns() + limit_ns;
+    for (uint32_t spin = 0;; ++spin) {
+        if ((int32_t)(ld_acquire_gpu(addr) - target) >= 0) {
+            return true;
+        }
+        __nanosleep(200);
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag != 0u || global_timer_ns() > deadline) {
+                return false;
+            }
+        }
+    }
+}
+
 // L2 eviction-priority policies for loads that carry a cache hint.
 __device__ __forceinline__ uint64_t l2_policy_evict_last()
 {

@@ -168,10 +168,13 @@ def test_split_k_with_k_fastest_in_the_schedule(sp, orc, cuda, split_k):
 
 
 @pytest.mark.parametrize("shape", [(1536, 2304, 8192), (512, 512, 4096), (16384, 64, 1024), (160, 480, 816),
-                                   (2048, 6000, 264), (300, 131, 2056), (256, 256, 64)])
+                                   (2048, 6000, 264), (300, 131, 2056), (256, 256, 64), (2560, 2560, 1024),
+                                   (2304, 2816, 2048), (1024, 4864, 512)])
 def test_stream_k(sp, orc, cuda, shape):
-    """split_k = -1: whole waves tile by tile, the K blocks of the last partial wave dealt out over all CTA
-    pairs (the reference's stream-K modes, gemm/gemm_sm90.cu:1004-1094)."""
+    """split_k = -1: whole waves tile by tile, the tiles of a last wave that is at most half full cut into
+    aligned K ranges that run at the same time and are reduce-added into tiles the kernel zeroes itself
+    (the reference's stream-K modes, gemm/gemm_sm90.cu:1004-1094).  The shapes cover tails with and without
+    whole waves before them, N % 4 != 0 (scalar zeroing and atomic adds) and tails that run whole."""
     M, N, K = shape
     a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
     for cta_group, block_n, max_ctas in ((2, 256, 0), (1, 128, 0), (2, 64, 20)):
@@ -179,6 +182,26 @@ def test_stream_k(sp, orc, cuda, shape):
         sp.matmul_sm100(a, b, c, block_n=block_n, cta_group=cta_group, split_k=-1, max_ctas=max_ctas)
         sp.status()
         _check(sp, orc, a, b, c, K)
+
+
+def test_stream_k_back_to_back(sp, orc, cuda):
+    """Stream-K launches one after the other with nothing between them (each may set itself up while the
+    previous one drains, and each meets at its own value of a device counter): every result is right, and
+    the library's own choice (split_k = 0) takes this path for 2.35 waves of tiles."""
+    import torch
+    M, N, K = 2560, 2560, 1024
+    assert sp.choice(M, N, 8 * K, split_k=0)["split_k"] == -1
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    cs = [_poisoned(cuda, M, N) for _ in range(20)]
+    for c in cs:
+        sp.matmul_sm100(a, b, c, block_n=256, cta_group=2, split_k=-1)
+    sp.status()
+    _check(sp, orc, a, b, cs[0], K)
+    for c in cs[1:]:
+        assert torch.equal(c, cs[0]) or float((c - cs[0]).abs().max()) < 1e-3  # reduce-add order may differ
+    whole = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, whole, block_n=256, cta_group=2, split_k=1)
+    assert float((whole - cs[-1]).abs().max()) < 1e-2
 
 
 @pytest.mark.parametrize("shape", [(16384, 64, 2048), (1000, 264, 136), (513, 128, 4104), (256, 256, 64), (300, 131, 200)])

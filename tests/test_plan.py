@@ -56,7 +56,8 @@ def test_split_k_is_normalised(L):
     ((8192, 8192, 8192), 256, 2, 1, 0), ((1536, 2304, 65536), 256, 2, -1, 0), ((16384, 64, 8192), 64, 2, -1, 0),
     ((160, 480, 816), 128, 1, -1, 0), ((2048, 6000, 264), 64, 2, -1, 20), ((1000, 264, 136), 256, 2, 1, 0),
     ((768, 768, 4096), 256, 1, 4, 0), ((300, 131, 2056), 128, 2, -1, 0), ((8192, 8192, 8192), 256, 2, -1, 0),
-    ((4096, 4096, 64), 128, 2, 3, 6),
+    ((4096, 4096, 64), 128, 2, 3, 6), ((4096, 4096, 4096), 256, 2, -1, 0), ((2304, 2816, 65536), 256, 2, -1, 0),
+    ((2048, 2048, 2048), 256, 2, -1, 0), ((512, 768, 1024), 256, 2, -1, 0),
     # 256 x 512 tiles, and split-K with K fastest in the schedule (gemm_sm90_k_mode::split_k_inner)
     ((8192, 8192, 8192), 512, 2, 1, 0), ((1000, 2050, 264), 512, 2, 3, 4), ((640, 1100, 2048), 256, 1, -3, 6),
     ((1536, 2304, 8192), 512, 2, -4, 0),
@@ -87,10 +88,19 @@ def test_every_k_block_of_every_tile_is_covered_exactly_once(L, shape, bn, cg, s
             second = _items(L, M, N, K, bn, cg, sk, 1, max_ctas)[0]
             assert first[:2] == second[:2] and second[2] == first[3]
     if p["sk_tiles"]:
-        assert len(reduce_tiles) == p["sk_tiles"]
-        loads = [sum(kb1 - kb0 for (_, _, kb0, kb1, red) in _items(L, M, N, K, bn, cg, sk, g, max_ctas) if red)
-                 for g in range(p["groups"])]
-        assert max(loads) - min(loads) <= 1  # the stream-K part is balanced to one K block
+        # stream-K: the tail tiles (fewer than groups) are cut into aligned K ranges, at most one per group
+        assert len(reduce_tiles) == p["sk_tiles"] < p["groups"] or p["dp_tiles"] == 0
+        assert p["sk_tiles"] * p["sk_extra"] <= p["groups"] and p["sk_extra"] >= 2
+        starts = set()
+        for g in range(p["groups"]):
+            red_items = [it for it in _items(L, M, N, K, bn, cg, sk, g, max_ctas) if it[4]]
+            assert len(red_items) <= 1
+            for (_, _, kb0, kb1, _) in red_items:
+                assert kb0 % p["sk_share"] == 0 and kb1 - kb0 <= p["sk_share"]
+                starts.add(kb0)
+        assert len(starts) == p["sk_extra"]  # every tile is cut at the same K offsets
+    elif sk == -1:
+        assert not reduce_tiles  # a tail that is more than half a wave runs whole
 
 
 def test_raster_keeps_concurrent_tiles_compact(L):
