@@ -32,10 +32,12 @@ enum class gemm_sm100_k_mode
     output_stationary,
     split_k_outer,
     split_k_inner,  // the K ranges of a tile are neighbours in the schedule (gemm_sm90_k_mode::split_k_inner)
-    stream_k,  // the last partial wave of tiles is cut along K over all CTA pairs (the schedule of both
-               // gemm_sm90_k_mode::stream_k_* flavours, which differ in code structure only).  Kept for
-               // parity of the mode list; `automatic` is the mode to use: it is faster on every shape measured.
-    automatic, // output_stationary, or split_k_outer with a split count chosen to fill the waves (few tiles, long K)
+    stream_k,  // whole waves run tile by tile; the tiles of a last wave that is at most half full are cut
+               // into aligned K ranges that run at the same time (the schedule of both
+               // gemm_sm90_k_mode::stream_k_* flavours, which differ in code structure only)
+    automatic, // output_stationary, split_k_outer with a split count chosen to fill the waves (few tiles, long
+               // K), or stream_k (several waves, the last one less than half full); with variant 0 the tile
+               // is the library's choice too
 };
 
 // The kernel takes the harness's hot operand layout: A row-major, B stored N x K (gemm/gemm_test.cu:365);
@@ -68,7 +70,9 @@ inline int matmul_sm100(GPU_TensorsF16 t, cudaStream_t stream, gemm_sm100_k_mode
                           : k_mode == gemm_sm100_k_mode::automatic   ? 0
                           : k_mode == gemm_sm100_k_mode::split_k_inner ? -split_k
                                                                         : split_k;
-        rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, 2, split, 0, stream);
+        // automatic without a variant: the library picks the tile as well as the K mode
+        const int cta_group = (k_mode == gemm_sm100_k_mode::automatic && variant == 0) ? 0 : 2;
+        rc = spork_gemm_sm100_f16f32_ex(t.M, t.N, t.K, t.a, t.b, t.c, block_n, cta_group, split, 0, stream);
     } else {
         rc = spork_gemm_sm100_f16f32(t.M, t.N, t.K, t.a, t.b, t.c, variant, stream);
     }

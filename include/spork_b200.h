@@ -69,7 +69,10 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
 /* Launch with every tunable explicit (benchmark sweeps and tests).
  *   block_n   64 / 128 / 256   output-tile width
  *   cta_group 1 = one CTA per tile (128 x block_n),
- *             2 = a CTA pair per tile (256 x block_n, tcgen05 cta_group::2)
+ *             2 = a CTA pair per tile (256 x block_n, tcgen05 cta_group::2),
+ *             0 = the tile is left to the library as in spork_gemm_sm100_f16f32
+ *             (block_n is then its `variant`, 0 allowed); with split_k = 0 this
+ *             is the fully automatic launch
  *   split_k   0: chosen by the library: 1, or, for a problem with fewer 256-wide
  *             output tiles than CTA pairs and a long K, the count that fills
  *             the waves best, or stream-K (-1) when the last of several waves

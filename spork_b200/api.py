@@ -166,7 +166,8 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
 
     ``variant`` 0/64/128/256 picks the output-tile width like the reference's
     n64/n128/n256 kernels.  ``block_n``/``cta_group``/``split_k``/``max_ctas``
-    select the explicit-tunables entry point instead.
+    select the explicit-tunables entry point instead; ``split_k=0`` alone leaves
+    tile and K mode (whole tiles, split-K or stream-K) to the library.
     """
     import torch
 
@@ -188,7 +189,10 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
             rc = lib().spork_gemm_sm100_f16f32(M, N, K, pa, pb, pc, variant, sp)
         else:
             bn = block_n if block_n is not None else (variant or (64 if N <= 64 else 128 if N <= 128 else 256))
-            rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cta_group or 2, split_k, max_ctas, sp)
+            cg = cta_group or 2
+            if block_n is None and cta_group is None and variant == 0 and split_k == 0:
+                cg = 0  # fully automatic: the library picks the tile and the K mode
+            rc = lib().spork_gemm_sm100_f16f32_ex(M, N, K, pa, pb, pc, bn, cg, split_k, max_ctas, sp)
     _check(rc, "spork_gemm_sm100_f16f32")
     return c
 

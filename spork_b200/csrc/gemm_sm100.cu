@@ -107,7 +107,42 @@ __device__ __forceinline__ void report_timeout(const Params& p, volatile uint32_
 // kWorkspace = true: each K split stores its partial tile into slab `split` of a
 // [split][M][N] fp32 workspace (tmap_c is then a 3-D map over it) instead of
 // writing or reduce-adding into C; a second kernel sums the slabs in a fixed order.
-template <int CG, int BLOCK_N, bool kWorkspace = false, bool kTf32 = false, int KATOMS = 1>
+// Stream-K tiles are accumulated by reduce-adds, so C must be zero there first.  The epilogue warps have
+// nothing to do until the first tile is complete: each zeroes its share of the rows (one tile row at a
+// time) and counts itself in; the count is checked before a warp's first reduce-add, whole tiles later.
+template <int TILE_M, int TILE_N>
+__device__ __forceinline__ void zero_stream_k_tiles(const Params& p, uint32_t warp_index, uint32_t warps_total, uint32_t lane)
+{
+    const uint32_t rows_total = p.sk_tiles * TILE_M;
+    for (uint32_t r = warp_index; r < rows_total; r += warps_total) {
+        WorkItem z;
+        decode_tile(p, p.dp_tiles + r / TILE_M, z);
+        const uint32_t row = z.m_tile * TILE_M + r % TILE_M;
+        const uint32_t col0 = z.n_tile * TILE_N;
+        if (row >= p.M || col0 >= p.N) {
+            continue;
+        }
+        const uint32_t cols = p.N - col0 < (uint32_t)TILE_N ? p.N - col0 : (uint32_t)TILE_N;
+        float* dst = p.C + (size_t)row * p.N + col0;
+        if (p.use_tma_store) {
+            // N % 4 == 0 and C is 16-byte aligned: so is every tile row
+            for (uint32_t c = lane * 4; c < cols; c += 128) {
+                *reinterpret_cast<float4*>(dst + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        } else {
+            for (uint32_t c = lane; c < cols; c += 32) {
+                dst[c] = 0.0f;
+            }
+        }
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+        red_release_gpu_add(p.sk_counter, 1u);
+    }
+}
+
+template <int CG, int BLOCK_N, bool kWorkspace = false, bool kTf32 = false, int KATOMS = 1, bool kStreamK = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_c, const Params p)
@@ -349,44 +384,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t local = 0;
         uint32_t slab_sel = 0;
         bool ok = true;
-        bool sk_zeroed = p.sk_tiles == 0;  // the stream-K tiles are known to be zero everywhere
-        if (p.sk_tiles != 0) {
-            // Stream-K tiles are accumulated by reduce-adds, so C must be zero there first.  The epilogue
-            // warps have nothing to do until the first tile is complete: each zeroes its share of the rows
-            // (one 256-column tile row = 1 KB at a time) and counts itself in; the count is checked before
-            // this warp's first reduce-add, whole tiles later.
-            const uint32_t warps_total = gridDim.x * kNumEpilogueWarps;
-            const uint32_t rows_total = p.sk_tiles * Cfg::kUmmaM;
-            for (uint32_t r = blockIdx.x * kNumEpilogueWarps + epi; r < rows_total; r += warps_total) {
-                WorkItem z;
-                decode_tile(p, p.dp_tiles + r / Cfg::kUmmaM, z);
-                const uint32_t row = z.m_tile * Cfg::kUmmaM + r % Cfg::kUmmaM;
-                const uint32_t col0 = z.n_tile * BLOCK_N;
-                if (row >= p.M || col0 >= p.N) {
-                    continue;
-                }
-                const uint32_t cols = p.N - col0 < (uint32_t)BLOCK_N ? p.N - col0 : (uint32_t)BLOCK_N;
-                float* dst = p.C + (size_t)row * p.N + col0;
-                if (p.use_tma_store) {
-                    // N % 4 == 0 and C is 16-byte aligned: so is every tile row
-                    for (uint32_t c = lane * 4; c < cols; c += 128) {
-                        *reinterpret_cast<float4*>(dst + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    }
-                } else {
-                    for (uint32_t c = lane; c < cols; c += 32) {
-                        dst[c] = 0.0f;
-                    }
-                }
-            }
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) {
-                red_release_gpu_add(p.sk_counter, 1u);
-            }
+        // kStreamK: the instance stream-K launches run.  The others carry none of its code: measured on a
+        // store-bound shape (32768 x 65536 x 48) the epilogue ran 15 % slower with it compiled in, unused.
+        bool sk_zeroed = !kStreamK || p.sk_tiles == 0;  // the stream-K tiles are known to be zero everywhere
+        if (kStreamK && p.sk_tiles != 0) {
+            zero_stream_k_tiles<Cfg::kUmmaM, BLOCK_N>(p, blockIdx.x * kNumEpilogueWarps + epi,
+                                                     gridDim.x * kNumEpilogueWarps, lane);
         }
         for (uint32_t item = 0; item < num_items && ok; ++item, ++local) {
             const WorkItem w = group_item(p, group_id, num_groups, item);
-            if (w.reduce && !sk_zeroed) {
+            if (kStreamK && w.reduce && !sk_zeroed) {
                 if (!counter_wait(p.sk_counter, p.sk_target, abort_flag)) {
                     if (lane == 0) {
                         report_timeout(p, abort_flag, 3, 0x48);
@@ -698,7 +705,11 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
                   bool split_inner = false)
 {
     using Cfg = Config<CG, BLOCK_N, KATOMS>;
+    // stream-K has instances of its own, with one column block per stage only: a request with two runs whole
+    constexpr bool kHasStreamK = KATOMS == 1;
+    stream_k = stream_k && kHasStreamK;
     auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS>;
+    auto kernel_sk = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS, kHasStreamK>;
     constexpr int kElemsK = kTf32 ? kBlockKTf32 : kBlockK;
     constexpr CUtensorMapDataType kOperandType = kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     constexpr uint32_t kOperandBytes = kTf32 ? 4 : 2;
@@ -708,6 +719,10 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     std::call_once(attr_once[dev.ordinal], [&] {
         attr_err[dev.ordinal] =
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (kHasStreamK && attr_err[dev.ordinal] == cudaSuccess) {
+            attr_err[dev.ordinal] =
+                cudaFuncSetAttribute(kernel_sk, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        }
     });
     if (attr_err[dev.ordinal] != cudaSuccess) {
         return (int)attr_err[dev.ordinal];
@@ -776,7 +791,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tune.no_early_launch ? 1 : 2;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, tmap_c, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, p.sk_tiles != 0 ? kernel_sk : kernel, tmap_a, tmap_b, tmap_c, p);
     return (int)e;
 }
 
@@ -1505,8 +1520,11 @@ extern "C" int spork_gemm_sm100_supports(uint32_t M, uint32_t N, uint32_t K)
 extern "C" int spork_gemm_sm100_f16f32_ex(uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, float* C,
                                           int block_n, int cta_group, int split_k, int max_ctas, void* stream)
 {
-    if (cta_group != 1 && cta_group != 2) {
-        return SPORK_ERR_BAD_ARGUMENT;  // this entry point is for explicit choices
+    if (cta_group < 0 || cta_group > 2 || (block_n == 0 && cta_group != 0)) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    if (block_n == 0) {
+        block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);  // the default entry point's starting width
     }
     return spork::gemm_sm100::dispatch(M, N, K, A, B, C, block_n, cta_group, split_k, max_ctas,
                                        static_cast<cudaStream_t>(stream));

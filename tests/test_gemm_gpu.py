@@ -204,6 +204,19 @@ def test_stream_k_back_to_back(sp, orc, cuda):
     assert float((whole - cs[-1]).abs().max()) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(2560, 2560, 8192), (768, 3072, 3072), (1536, 2304, 8192), (8192, 4096, 4096),
+                                   (300, 131, 2056)])
+def test_fully_automatic_launch(sp, orc, cuda, shape):
+    """split_k = 0 with no tile given: the library picks tile width and K mode (whole tiles, split-K or
+    stream-K); whatever it picks, the product is right."""
+    M, N, K = shape
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    c = _poisoned(cuda, M, N)
+    sp.matmul_sm100(a, b, c, split_k=0)
+    sp.status()
+    _check(sp, orc, a, b, c, K)
+
+
 @pytest.mark.parametrize("shape", [(16384, 64, 2048), (1000, 264, 136), (513, 128, 4104), (256, 256, 64), (300, 131, 200)])
 def test_two_column_blocks_per_stage(sp, orc, cuda, shape):
     """The ring-stage variant chosen for skinny problems (256-byte row segments per TMA request), forced on

@@ -177,3 +177,14 @@ def test_tile_narrows_when_256_wide_tiles_underfill_the_machine(sp):
         assert c(768, 3072, 3072)["block_n"] == 256
     finally:
         sp.tune()
+
+
+def test_automatic_mode_picks_stream_k_for_a_thin_last_wave(sp):
+    """split_k = 0 resolves to stream-K (-1) when several waves of 256-wide tiles end in a wave that is less
+    than half full and the modelled gain is at least 7 %; otherwise tiles run whole."""
+    assert sp.choice(4096, 4096, 4096, split_k=0)["split_k"] == -1      # 3 waves + 34 of 74
+    assert sp.choice(2304, 2816, 65536, split_k=0)["split_k"] == -1     # 1 wave + 25 of 74
+    assert sp.choice(8192, 8192, 2048, split_k=0)["split_k"] == 1       # 13 waves + 62 of 74: runs whole
+    assert sp.choice(4096, 4096, 1024, split_k=0)["split_k"] == 1       # K too short to pay for the reduce-adds
+    assert sp.choice(4096, 4096, 4096, split_k=1)["split_k"] == 1       # the caller asked for whole tiles
+    assert sp.choice(4096, 4096, 4096, split_k=0, sm_count=128)["split_k"] == 1  # 256 tiles = 4 full waves of 64
