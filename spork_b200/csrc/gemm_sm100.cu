@@ -944,6 +944,12 @@ static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int b
         if (!tf32 && split_k == 1 && K <= 1024 && pair_tiles * 4 <= (uint64_t)sm_count) {
             cta_group = 1;
             block_n = block_n > 128 ? 128 : block_n;
+        } else if (!tf32 && split_k <= 1 && K <= 256 && pair_tiles >= (uint64_t)sm_count) {
+            // A large problem with at most four K blocks per tile is bound by writing C.  Single CTAs then
+            // store faster than pairs, whose epilogues wait for each other at every tile (16384 x 16384 x K,
+            // GB/s of C written: K = 64 5460 against 5050, 128 5720 / 5060, 256 5550 / 4690; K = 512 equal;
+            // from K = 816 on the pair's halved operand traffic wins, 2870 against 2350).
+            cta_group = 1;
         }
     }
     if (split_k == 0) {

@@ -38,7 +38,7 @@ CHILD = textwrap.dedent("""
         sp.init_test_data(a, sp.DATA_UNIFORM_PM1, sp.SEED_A); sp.init_test_data(b, sp.DATA_UNIFORM_PM1, sp.SEED_B, transpose_rule=True)
         return a, b
     cases = [((300, 200, 264), dict(block_n=64, cta_group=1)), ((513, 1028, 200), dict(block_n=256, cta_group=2)),
-             ((512, 512, 2048), dict(block_n=128, cta_group=2, split_k=3)), ((1536, 2304, 1024), dict(block_n=256, cta_group=2, split_k=-1)),
+             ((512, 512, 2048), dict(block_n=128, cta_group=2, split_k=3)), ((2560, 2560, 512), dict(block_n=256, cta_group=2, split_k=-1)),
              ((700, 1500, 1032), dict(block_n=512, cta_group=2)), ((130, 67, 72), dict(block_n=128, cta_group=2)),
              ((1000, 2050, 264), dict(block_n=512, cta_group=2, split_k=2))]
     for (M, N, K), kw in cases:

@@ -188,3 +188,14 @@ def test_automatic_mode_picks_stream_k_for_a_thin_last_wave(sp):
     assert sp.choice(4096, 4096, 1024, split_k=0)["split_k"] == 1       # K too short to pay for the reduce-adds
     assert sp.choice(4096, 4096, 4096, split_k=1)["split_k"] == 1       # the caller asked for whole tiles
     assert sp.choice(4096, 4096, 4096, split_k=0, sm_count=128)["split_k"] == 1  # 256 tiles = 4 full waves of 64
+
+
+def test_store_bound_problems_run_on_single_ctas(sp):
+    """Many tiles and at most four K blocks: the launch is bound by writing C, and single CTAs store faster
+    than pairs; from K = 512 on the pair tile stays."""
+    c = sp.choice(32768, 65536, 48)
+    assert (c["cta_group"], c["block_n"], c["split_k"]) == (1, 256, 1)
+    assert sp.choice(16384, 16384, 256)["cta_group"] == 1
+    assert sp.choice(16384, 16384, 512)["cta_group"] == 2
+    assert sp.choice(2048, 2048, 128)["cta_group"] == 2     # 64 pair tiles: not store-bound, latency-bound
+    assert sp.choice(16384, 16384, 128, tf32=True)["cta_group"] == 2   # tf32 has CTA-pair kernels only
