@@ -35,10 +35,6 @@ struct Params {
     // kernel itself zeroes there at its start.
     uint32_t dp_tiles, sk_tiles;
     uint32_t sk_share, sk_extra; // K blocks per range, ranges per tile
-    uint32_t sk_balanced;        // 1: a problem of one tile column with fewer tiles than CTA groups (the skinny,
-                                 // HBM-bound shapes, where tiles share no operand strips): the K blocks of all
-                                 // tiles are dealt out evenly instead, group g owning sk_share (+1 if g < sk_extra)
-                                 // consecutive ones, which touch one or two (rarely three) tiles
     uint32_t sk_target;          // value of *sk_counter (modulo 2^32) from which every share is zeroed
     uint32_t wide_skew;          // 256 x 512 tiles: K blocks of one accumulator half issued ahead of the other at both
                                  // ends of a tile (1 .. ring depth)
@@ -90,14 +86,6 @@ SPORK_HD uint32_t group_item_count(const Params& p, uint32_t g, uint32_t G)
         return items > g ? (items - g - 1) / G + 1 : 0;
     }
     const uint32_t n1 = p.dp_tiles / G;  // dp_tiles is a multiple of G
-    if (p.sk_balanced) {
-        const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-        if (cnt == 0) {
-            return n1;
-        }
-        const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-        return n1 + ((u0 + cnt - 1) / p.num_kb - u0 / p.num_kb + 1);
-    }
     return n1 + (g < p.sk_tiles * p.sk_extra ? 1u : 0u);
 }
 
@@ -129,18 +117,6 @@ SPORK_HD WorkItem group_item(const Params& p, uint32_t g, uint32_t G, uint32_t i
         w.kb_begin = 0;
         w.kb_end = p.num_kb;
         w.reduce = false;
-        return w;
-    }
-    if (p.sk_balanced) {
-        const uint32_t cnt = p.sk_share + (g < p.sk_extra ? 1u : 0u);
-        const uint32_t u0 = g * p.sk_share + (g < p.sk_extra ? g : p.sk_extra);
-        const uint32_t rel = u0 / p.num_kb + (i - n1);   // tile index inside the stream-K part
-        const uint32_t t0 = rel * p.num_kb;              // its first K-block unit
-        decode_tile(p, p.dp_tiles + rel, w);
-        w.kb_begin = u0 > t0 ? u0 - t0 : 0;
-        const uint32_t u1 = u0 + cnt;
-        w.kb_end = u1 < t0 + p.num_kb ? u1 - t0 : p.num_kb;
-        w.reduce = true;
         return w;
     }
     // the group's one stream-K item: ranges of one tile sit sk_tiles groups apart
@@ -250,17 +226,7 @@ inline void plan_launch(Params& p, uint32_t& groups, uint32_t M, uint32_t N, uin
         kb_per_range = kb_per_range < 4 ? 4 : kb_per_range;
         ranges = (p.num_kb + kb_per_range - 1) / kb_per_range;  // no empty ranges
     }
-    p.sk_balanced = 0;
-    if (stream_k && p.split_k == 1 && ranges <= 1 && p.tiles_n == 1 && tiles < groups &&
-        (uint64_t)tiles * p.num_kb >= 8ull * groups) {
-        // one tile column, fewer tiles than groups, a long K: every group gets an equal run of K blocks
-        p.dp_tiles = 0;
-        p.sk_tiles = tiles;
-        const uint32_t units = tiles * p.num_kb;
-        p.sk_share = units / groups;
-        p.sk_extra = units % groups;
-        p.sk_balanced = 1;
-    } else if (stream_k && p.split_k == 1 && ranges > 1) {
+    if (stream_k && p.split_k == 1 && ranges > 1) {
         // whole waves run tile by tile; the tiles of the last partial wave are cut into aligned K ranges
         p.dp_tiles = tiles - tail;
         p.sk_tiles = tail;

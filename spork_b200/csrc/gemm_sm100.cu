@@ -706,7 +706,7 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
 {
     using Cfg = Config<CG, BLOCK_N, KATOMS>;
     // stream-K has instances of its own (not for every ring-stage variant: a request without one runs whole)
-    constexpr bool kHasStreamK = KATOMS == 1 || (KATOMS == 2 && CG == 2);
+    constexpr bool kHasStreamK = KATOMS == 1;
     stream_k = stream_k && kHasStreamK;
     auto kernel = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS>;
     auto kernel_sk = gemm_kernel<CG, BLOCK_N, false, kTf32, KATOMS, kHasStreamK>;
@@ -1003,19 +1003,6 @@ static bool choose_tile(TileChoice& c, uint32_t M, uint32_t N, uint32_t K, int b
             if (t_stream * 100 < t_whole * 93) {
                 split_k = -1;
             }
-        }
-    }
-    if (split_left_to_library && split_k == 1 && cta_group == 2 && batches == 1 && N <= (uint32_t)block_n && K >= 2048) {
-        // One column of tiles, fewer of them than CTA pairs (16384 x 64..256 x 8192: 64 tiles for 74 pairs):
-        // the launch streams A from HBM once and every SM's share of that stream counts.  Stream-K deals the
-        // K blocks out evenly over all pairs (plan_launch: the balanced partition).
-        uint32_t groups = (uint32_t)sm_count / 2u;
-        if (max_ctas > 0 && (uint32_t)max_ctas / 2u < groups) {
-            groups = (uint32_t)max_ctas / 2u;
-        }
-        const uint32_t tiles = (M + 255) / 256;
-        if (tiles < groups && tiles * 2 > groups) {
-            split_k = -1;
         }
     }
     // Two column blocks per stage for skinny problems (few output tiles, long K): their time goes into

@@ -57,8 +57,7 @@ def test_split_k_is_normalised(L):
     ((160, 480, 816), 128, 1, -1, 0), ((2048, 6000, 264), 64, 2, -1, 20), ((1000, 264, 136), 256, 2, 1, 0),
     ((768, 768, 4096), 256, 1, 4, 0), ((300, 131, 2056), 128, 2, -1, 0), ((8192, 8192, 8192), 256, 2, -1, 0),
     ((4096, 4096, 64), 128, 2, 3, 6), ((4096, 4096, 4096), 256, 2, -1, 0), ((2304, 2816, 65536), 256, 2, -1, 0),
-    ((2048, 2048, 2048), 256, 2, -1, 0), ((512, 768, 1024), 256, 2, -1, 0), ((16384, 128, 8192), 128, 2, -1, 0),
-    ((16384, 256, 8192), 256, 2, -1, 0), ((3000, 100, 4096), 128, 1, -1, 40),
+    ((2048, 2048, 2048), 256, 2, -1, 0), ((512, 768, 1024), 256, 2, -1, 0),
     # 256 x 512 tiles, and split-K with K fastest in the schedule (gemm_sm90_k_mode::split_k_inner)
     ((8192, 8192, 8192), 512, 2, 1, 0), ((1000, 2050, 264), 512, 2, 3, 4), ((640, 1100, 2048), 256, 1, -3, 6),
     ((1536, 2304, 8192), 512, 2, -4, 0),
@@ -88,14 +87,7 @@ def test_every_k_block_of_every_tile_is_covered_exactly_once(L, shape, bn, cg, s
         if p["groups"] > 1:
             second = _items(L, M, N, K, bn, cg, sk, 1, max_ctas)[0]
             assert first[:2] == second[:2] and second[2] == first[3]
-    balanced = bool(p["sk_tiles"]) and p["tiles_n"] == 1 and p["dp_tiles"] == 0 and 2 * p["sk_tiles"] > p["groups"]
-    if balanced:
-        # one column of tiles, a few fewer than groups: every group owns an equal run of K blocks
-        loads = [sum(kb1 - kb0 for (_, _, kb0, kb1, red) in _items(L, M, N, K, bn, cg, sk, g, max_ctas) if red)
-                 for g in range(p["groups"])]
-        assert max(loads) - min(loads) <= 1 and min(loads) >= 8
-        assert len(reduce_tiles) == p["sk_tiles"] == p["tiles_m"]
-    elif p["sk_tiles"]:
+    if p["sk_tiles"]:
         # stream-K: the tail tiles (fewer than groups) are cut into aligned K ranges, at most one per group
         assert len(reduce_tiles) == p["sk_tiles"] < p["groups"] or p["dp_tiles"] == 0
         assert p["sk_tiles"] * p["sk_extra"] <= p["groups"] and p["sk_extra"] >= 2
