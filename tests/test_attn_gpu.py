@@ -322,3 +322,28 @@ def test_headline_size_heads_against_the_oracle(sp, orc, cuda):
     _, ref = orc.attn_causal_f16(q[77:78].cpu().numpy(), k[77:78].cpu().numpy(), v[77:78].cpu().numpy())
     ok, worst = _close(o[77:78].cpu().numpy(), ref)
     assert ok, f"causal head 77: max abs error {worst}"
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_sizes_masks_and_scales(sp, orc, cuda, seed):
+    """A seeded sweep nobody chose by hand: ragged sequence lengths around the 128-key block and the 256-row
+    CTA, both head dimensions, with and without the causal mask (each query tile then ends at its own
+    diagonal block), the default and a random softmax scale."""
+    import torch
+
+    rng = np.random.RandomState(seed)
+    for _ in range(8):
+        BH = int(rng.randint(1, 5))
+        S = int(rng.choice([rng.randint(1, 130), rng.randint(130, 520), rng.randint(520, 1300)]))
+        D = int(rng.choice([64, 128]))
+        causal = bool(rng.randint(0, 2))
+        scale = None if rng.randint(0, 2) else float(rng.uniform(0.02, 0.3))
+        q, k, v = _qkv(sp, cuda, BH, S, D, seed=int(rng.randint(1, 1 << 20)))
+        o = torch.full((BH, S, D), float("nan"), dtype=torch.float16, device=cuda)
+        sp.attn_fwd(q, k, v, o, causal=causal, **({} if scale is None else {"scale": scale}))
+        sp.status()
+        fn = orc.attn_causal_f16 if causal else orc.attn_f16
+        args = (q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+        _, ref = fn(*args) if scale is None else fn(*args, scale=scale)
+        ok, worst = _close(o.cpu().numpy(), ref)
+        assert ok, f"BH={BH} S={S} D={D} causal={causal} scale={scale}: max abs error {worst}"
