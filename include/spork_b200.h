@@ -229,8 +229,9 @@ int spork_gemm_sm100_tuning(int* out, int capacity);
 /* Host-only view of how a launch would be laid out (no CUDA call; usable without a
  * GPU).  Arguments as for the _ex entry point, plus the SM count to plan for and
  * tf32 (0/1).  out[10] = tiles_m, tiles_n, K blocks, splits, K blocks per split,
- * CTA groups (CTAs / cta_group), whole-tile count, stream-K tile count, stream-K
- * share per group, groups that get one extra block.  The reference computes the
+ * CTA groups (CTAs / cta_group), whole-tile count, stream-K tile count, K blocks
+ * per stream-K range, ranges per stream-K tile.  split_k = 0 resolves the split
+ * count only (stream-K is chosen in spork_gemm_sm100_choice).  The reference computes the
  * equivalent inside its kernel (gemm/gemm_sm90.cu:1004-1129). */
 int spork_gemm_sm100_plan(uint32_t M, uint32_t N, uint32_t K, int block_n, int cta_group, int split_k, int max_ctas,
                           int sm_count, int tf32, uint32_t* out);

@@ -104,3 +104,26 @@ def test_tf32_argument_errors(sp, cuda):
     assert L.spork_gemm_sm100_tf32f32(128, 128, 68, a.data_ptr(), a.data_ptr(), c.data_ptr(), 96, 1, None) == 10001
     assert L.spork_gemm_sm100_tf32f32(128, 128, 68, None, a.data_ptr(), c.data_ptr(), 0, 1, None) == 10001
     sp.status()
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_tf32_random_shapes_and_modes(sp, orc, cuda, seed):
+    """A seeded sweep over ragged shapes (K a multiple of 4 only), tile variants and K modes of the tf32 path,
+    including the automatic launch and stream-K on a problem with a thin last wave."""
+    rng = np.random.RandomState(seed)
+    cases = [(2560, 2560, 1024, dict(split_k=0))]   # 100 tiles: one wave of 74 + 26 cut in two (stream-K)
+    for _ in range(7):
+        M = int(rng.choice([rng.randint(1, 300), rng.randint(300, 1500)]))
+        N = int(rng.choice([rng.randint(1, 200), rng.randint(200, 1300)]))
+        K = 4 * int(rng.choice([rng.randint(1, 40), rng.randint(40, 500)]))
+        kw = dict(variant=int(rng.choice([0, 64, 128, 256, 512])), split_k=int(rng.choice([1, 1, 2, 3, 0])))
+        cases.append((M, N, K, kw))
+    for (M, N, K, kw) in cases:
+        a, b = _rand(M, K, seed * 100 + 1), _rand(N, K, seed * 100 + 2)
+        c = sp.matmul_sm100_tf32(a.to(cuda), b.to(cuda), **kw)
+        sp.status()
+        if M * N * K <= 1 << 29:
+            ref = orc.gemm_f32(a.numpy(), b.numpy(), 0)
+        else:
+            ref = (a.double() @ b.double().t()).float().numpy()
+        assert orc.normalised_error(c.cpu().numpy(), ref, 1.0, 1.0, K) <= 1.0, (M, N, K, kw)
