@@ -204,6 +204,26 @@ def test_stream_k_back_to_back(sp, orc, cuda):
     assert float((whole - cs[-1]).abs().max()) < 1e-2
 
 
+def test_stream_k_launches_of_different_shapes_in_a_row(sp, orc, cuda):
+    """Stream-K launches of different grids and partitions one after the other in one stream: the counters
+    their CTAs meet at are handed out in rotation and never reset, so every launch must find its own count."""
+    shapes = [(2560, 2560, 1024), (512, 512, 4096), (300, 131, 2056), (2304, 2816, 512)]
+    data = []
+    for (M, N, K) in shapes:
+        a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+        data.append((a, b, sp.gemm_baseline(a, b), K))
+    for _ in range(12):
+        outs = []
+        for (a, b, ref, K) in data:
+            c = _poisoned(cuda, *ref.shape)
+            sp.matmul_sm100(a, b, c, block_n=256, cta_group=2, split_k=-1)
+            outs.append(c)
+        sp.status()
+        for (a, b, ref, K), c in zip(data, outs):
+            _, max_diff = sp.compare_f32(ref, c)
+            assert max_diff / (K * 2.0 ** -10) < 1e-2, (tuple(ref.shape), K, max_diff)
+
+
 @pytest.mark.parametrize("shape", [(2560, 2560, 8192), (768, 3072, 3072), (1536, 2304, 8192), (8192, 4096, 4096),
                                    (300, 131, 2056)])
 def test_fully_automatic_launch(sp, orc, cuda, shape):
