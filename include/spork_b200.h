@@ -92,7 +92,8 @@ int spork_gemm_sm100_tf32f32(uint32_t M, uint32_t N, uint32_t K, const float* A,
  *             are reduce-added into C.  The kernel zeroes those tiles itself
  *             while its epilogue warps wait for the first tile, and its CTAs
  *             meet at a device counter before the first reduce-add (a bounded
- *             wait): the launch relies on all its CTAs being resident
+ *             wait; the last CTA to leave resets the counter, so a launch can
+ *             be replayed from a CUDA graph): the launch relies on all its CTAs being resident
  *             together, which holds when it has the device to itself, so do
  *             not run stream-K launches of several streams at the same time.
  *             A last wave more than half full runs whole (no ranges).
@@ -207,6 +208,14 @@ int spork_gemm_sm100_choice(uint32_t M, uint32_t N, uint32_t K, int variant, int
  * look-ups of the process hit and missed that cache.  The reference encodes them
  * on every launch (gemm/gemm_sm90.cu:1167-1206). */
 int spork_gemm_sm100_tmap_cache_stats(uint64_t* hits, uint64_t* misses);
+
+/* The counter pairs stream-K launches meet at, read back after `stream` has
+ * drained: out[32] = (warps that zeroed their share, CTAs that left) of each of
+ * the 16 pairs.  Every pair is back at zero whenever no stream-K launch is in
+ * flight: the last CTA to leave resets it, which is what makes the value a launch
+ * waits for independent of earlier launches.  Diagnostic; no counterpart in the
+ * reference. */
+int spork_gemm_sm100_stream_k_counters(uint32_t* out, void* stream);
 
 /* Tracing of the 256 x 512 kernel: later launches make their first CTA write SM
  * clock stamps (clock64) of its tile hand-overs into `device_buffer`, eight

@@ -33,6 +33,7 @@ from .api import (  # noqa: F401
     status,
     ring_model,
     tmap_cache_stats,
+    stream_k_counters,
     trace,
     tune,
     tuning,

@@ -87,6 +87,8 @@ def lib() -> ctypes.CDLL:
         L.spork_gemm_sm100_choice.restype = i32
         L.spork_gemm_sm100_tmap_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
         L.spork_gemm_sm100_tmap_cache_stats.restype = i32
+        L.spork_gemm_sm100_stream_k_counters.argtypes = [ctypes.POINTER(u32), vp]
+        L.spork_gemm_sm100_stream_k_counters.restype = i32
         L.spork_gemm_sm100_trace.argtypes = [vp, u32]
         L.spork_gemm_sm100_trace.restype = i32
         L.spork_gemm_sm100_tuning.argtypes = [ctypes.POINTER(i32), i32]
@@ -287,6 +289,14 @@ def tmap_cache_stats() -> tuple[int, int]:
     h, m = ctypes.c_uint64(0), ctypes.c_uint64(0)
     _check(lib().spork_gemm_sm100_tmap_cache_stats(ctypes.byref(h), ctypes.byref(m)), "spork_gemm_sm100_tmap_cache_stats")
     return int(h.value), int(m.value)
+
+
+def stream_k_counters(stream=None) -> list[tuple[int, int]]:
+    """The 16 counter pairs stream-K launches meet at, after ``stream`` has drained: all zero unless a launch
+    gave up half way (see spork_gemm_sm100_stream_k_counters)."""
+    out = (ctypes.c_uint32 * 32)()
+    _check(lib().spork_gemm_sm100_stream_k_counters(out, _stream_ptr(stream)), "spork_gemm_sm100_stream_k_counters")
+    return [(int(out[2 * i]), int(out[2 * i + 1])) for i in range(16)]
 
 
 def trace(buffer=None) -> None:

@@ -35,7 +35,7 @@ int current_device_state(DeviceState** out)
             return (int)e;
         }
         // 256 bytes: [0] status word, [16..48) clock probe of the last GEMM launch (see gemm_sm100.cu),
-        // [128..192) the stream-K counters
+        // [128..256) the stream-K counter pairs
         uint32_t* word = nullptr;
         e = cudaMalloc(&word, 256);
         if (e != cudaSuccess) {
@@ -55,23 +55,18 @@ int current_device_state(DeviceState** out)
     return 0;
 }
 
-void reserve_sk_counter(DeviceState& dev, uint32_t arrivals, uint32_t** counter, uint32_t* target)
+uint32_t* reserve_sk_counter(DeviceState& dev)
 {
     std::lock_guard<std::mutex> lock(dev.sk_mutex);
     const uint32_t slot = dev.sk_next++ % (uint32_t)DeviceState::kSkCounters;
-    dev.sk_reached[slot] += arrivals;  // modulo 2^32, like the counter itself
-    *counter = dev.status_word + DeviceState::kSkCounterWord0 + slot;
-    *target = dev.sk_reached[slot];
+    return dev.status_word + DeviceState::kSkCounterWord0 + 2 * slot;
 }
 
 void reset_sk_counters(DeviceState& dev, cudaStream_t stream)
 {
     std::lock_guard<std::mutex> lock(dev.sk_mutex);
-    cudaMemsetAsync(dev.status_word + DeviceState::kSkCounterWord0, 0, sizeof(uint32_t) * DeviceState::kSkCounters,
-                    stream);
-    for (int i = 0; i < DeviceState::kSkCounters; ++i) {
-        dev.sk_reached[i] = 0;
-    }
+    cudaMemsetAsync(dev.status_word + DeviceState::kSkCounterWord0, 0,
+                    sizeof(uint32_t) * 2 * DeviceState::kSkCounters, stream);
 }
 
 int ensure_staging(DeviceState& dev, int slot, size_t bytes)

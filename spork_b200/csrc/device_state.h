@@ -25,15 +25,14 @@ struct DeviceState {
     int sm_count = 0;
     int cc_major = 0;
     uint32_t* status_word = nullptr;  // device memory, zero = healthy
-    // Counters the CTAs of a stream-K launch meet at (device memory behind the status word, never reset:
-    // a launch is handed the value its counter will have reached once all of its warps have arrived).
-    // Launches take the counters in rotation, so launches that overlap (other streams) do not share one
-    // unless more than kSkCounters are in flight.
+    // Counter pairs the CTAs of a stream-K launch meet at (device memory behind the status word): [0] counts
+    // the warps that have zeroed their share, [1] the CTAs that have left; the last one to leave zeroes both.
+    // Launches take the pairs in rotation, so launches that overlap (other streams) do not share one unless
+    // more than kSkCounters are in flight.
     static constexpr int kSkCounters = 16;
     static constexpr int kSkCounterWord0 = 32;
     std::mutex sk_mutex;
     uint32_t sk_next = 0;
-    uint32_t sk_reached[kSkCounters] = {};
     // Staging buffers of the htod entry points (grown on demand, never shrunk).
     void* staging[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t staging_bytes[4] = {0, 0, 0, 0};
@@ -51,10 +50,10 @@ int current_device_state(DeviceState** out);
 // Create the pipeline streams and events of `dev` on first use; returns 0 or a cudaError_t.
 int ensure_pipeline(DeviceState& dev);
 
-// Hand a stream-K launch its counter and the value that means "all `arrivals` have arrived".
-void reserve_sk_counter(DeviceState& dev, uint32_t arrivals, uint32_t** counter, uint32_t* target);
+// Hand a stream-K launch its pair of counters.
+uint32_t* reserve_sk_counter(DeviceState& dev);
 
-// After a launch gave up (its arrivals may be incomplete): counters and their expected values back to zero.
+// After a launch gave up (its counters may be left non-zero): all counters back to zero.
 void reset_sk_counters(DeviceState& dev, cudaStream_t stream);
 
 // Grow staging buffer `slot` of `dev` to at least `bytes`; returns 0 or a cudaError_t.

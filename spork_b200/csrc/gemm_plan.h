@@ -35,7 +35,7 @@ struct Params {
     // kernel itself zeroes there at its start.
     uint32_t dp_tiles, sk_tiles;
     uint32_t sk_share, sk_extra; // K blocks per range, ranges per tile
-    uint32_t sk_target;          // value of *sk_counter (modulo 2^32) from which every share is zeroed
+    uint32_t sk_target;          // value of sk_counter[0] from which every share is zeroed: the grid's epilogue warps
     uint32_t wide_skew;          // 256 x 512 tiles: K blocks of one accumulator half issued ahead of the other at both
                                  // ends of a tile (1 .. ring depth)
     uint32_t experiment;         // diagnostics: bit 3 (256 x 512 kernel, results unchanged) = plain stores instead of TMA
@@ -46,7 +46,8 @@ struct Params {
     float* C;
     uint32_t* status;            // device status word
     unsigned long long* trace;   // optional (256 x 512 kernel): SM-clock stamps of CTA 0's tile hand-overs, 8 per work item
-    uint32_t* sk_counter;        // counts the warps that have finished zeroing their share of the stream-K tiles
+    uint32_t* sk_counter;        // [0] counts the warps that have finished zeroing their share of the stream-K tiles,
+                                 // [1] the CTAs that have left; the last one to leave zeroes both
 };
 // The kernels take three 128-byte tensor maps and this block.  Measured: with more than 512 bytes of kernel
 // parameters a launch bound by its TMA stores (32768 x 65536 x 48) runs 15 % slower (1.93 ms against 1.67 ms,

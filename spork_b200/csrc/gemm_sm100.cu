@@ -531,6 +531,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         probe[2] = (unsigned long long)clock64();
         probe[3] = global_timer_ns();
     }
+    if (kStreamK && p.sk_tiles != 0 && threadIdx.x == 0) {
+        // The last CTA to leave puts the launch's two counters back to zero (every CTA is past its check of
+        // the first one by now), so the next launch that is handed them starts from zero whatever it is:
+        // the value a launch waits for is then a property of its grid, not of the launches before it.
+        __threadfence();
+        if (atomicAdd(p.sk_counter + 1, 1u) == gridDim.x - 1u) {
+            p.sk_counter[0] = 0u;
+            p.sk_counter[1] = 0u;
+            __threadfence();
+        }
+    }
 }
 
 }  // namespace gemm_sm100
@@ -772,8 +783,9 @@ static int launch(uint32_t M, uint32_t N, uint32_t K, const void* A, const void*
     }
 
     if (p.sk_tiles != 0) {
-        // the kernel zeroes the stream-K tiles itself; its CTAs meet at one of the device's counters
-        reserve_sk_counter(dev, groups * CG * kNumEpilogueWarps, &p.sk_counter, &p.sk_target);
+        // the kernel zeroes the stream-K tiles itself; its CTAs meet at one of the device's counter pairs
+        p.sk_counter = reserve_sk_counter(dev);
+        p.sk_target = groups * CG * kNumEpilogueWarps;
     }
 
     cudaLaunchConfig_t cfg{};
@@ -1490,6 +1502,25 @@ extern "C" int spork_gemm_sm100_tmap_cache_stats(uint64_t* hits, uint64_t* misse
     *hits = spork::gemm_sm100::g_tmap_hits.load();
     *misses = spork::gemm_sm100::g_tmap_misses.load();
     return 0;
+}
+
+extern "C" int spork_gemm_sm100_stream_k_counters(uint32_t* out, void* stream)
+{
+    if (!out) {
+        return SPORK_ERR_BAD_ARGUMENT;
+    }
+    spork::DeviceState* dev = nullptr;
+    const int rc = spork::current_device_state(&dev);
+    if (rc) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(out, dev->status_word + spork::DeviceState::kSkCounterWord0,
+                                    sizeof(uint32_t) * 2 * spork::DeviceState::kSkCounters, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(s);
+    }
+    return (int)e;
 }
 
 extern "C" int spork_gemm_sm100_trace(void* device_buffer, uint32_t items)

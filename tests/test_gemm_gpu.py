@@ -204,6 +204,43 @@ def test_stream_k_back_to_back(sp, orc, cuda):
     assert float((whole - cs[-1]).abs().max()) < 1e-2
 
 
+def test_stream_k_counters_return_to_zero_and_launches_replay_from_a_graph(sp, orc, cuda):
+    """The last CTA of a stream-K launch to leave resets the launch's counter pair, so the value a launch
+    waits for depends on its grid only: after any number of launches every pair reads zero, and a launch
+    recorded into a CUDA graph can be replayed (its parameters are fixed at capture)."""
+    import torch
+
+    M, N, K = 2560, 2560, 1024
+    a, b = _inputs(sp, orc, cuda, M, N, K, orc.DATA_UNIFORM_PM1, orc.DATA_UNIFORM_PM1)
+    ref = sp.gemm_baseline(a, b)
+    for _ in range(40):   # more launches than there are counter pairs
+        c = sp.matmul_sm100(a, b, block_n=256, cta_group=2, split_k=-1)
+    sp.status()
+    assert all(pair == (0, 0) for pair in sp.stream_k_counters())
+    _, max_diff = sp.compare_f32(ref, c)
+    assert max_diff / (K * 2.0 ** -10) < 1e-2
+    # graph replay: capture one launch on a side stream, replay it into a poisoned result several times
+    c = _poisoned(cuda, M, N)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.stream(side):
+            sp.matmul_sm100(a, b, c, block_n=256, cta_group=2, split_k=-1)   # warm: attributes, tensor maps
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                sp.matmul_sm100(a, b, c, block_n=256, cta_group=2, split_k=-1, stream=side)
+    except (RuntimeError, sp.SporkError) as e:
+        pytest.skip(f"this launch cannot be captured here: {e}")
+    for _ in range(5):
+        c.view(torch.uint8).fill_(0x7D)
+        graph.replay()
+        torch.cuda.synchronize()
+        _, max_diff = sp.compare_f32(ref, c)
+        assert max_diff / (K * 2.0 ** -10) < 1e-2
+    sp.status()
+    assert all(pair == (0, 0) for pair in sp.stream_k_counters())
+
+
 def test_stream_k_launches_of_different_shapes_in_a_row(sp, orc, cuda):
     """Stream-K launches of different grids and partitions one after the other in one stream: the counters
     their CTAs meet at are handed out in rotation and never reset, so every launch must find its own count."""
