@@ -150,6 +150,30 @@ def _dev_ptr(t, dtype, what: str) -> int:
     return int(t.data_ptr())
 
 
+class _OnDevice:
+    """``with _OnDevice(t.device)``: the launch runs with that GPU current.  Nothing is switched (and nothing
+    is paid) when it already is, the usual case."""
+
+    __slots__ = ("_ctx",)
+
+    def __init__(self, device):
+        import torch
+
+        index = device if isinstance(device, int) else torch.device(device).index
+        current = torch.cuda.current_device()
+        self._ctx = None if index is None or index == current else torch.cuda.device(index)
+
+    def __enter__(self):
+        if self._ctx is not None:
+            self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            return self._ctx.__exit__(*exc)
+        return False
+
+
 def _same_device(first, *others) -> None:
     """All operands of a launch must live on one GPU: the kernel runs on the first one's device and would
     otherwise read or write addresses that mean nothing there."""
@@ -185,7 +209,7 @@ def matmul_sm100(a, b, c=None, *, variant: int = 0, block_n: int | None = None, 
     pa = _dev_ptr(a, torch.float16, "a")
     pb = _dev_ptr(b, torch.float16, "b")
     pc = _dev_ptr(c, torch.float32, "c")
-    with torch.cuda.device(a.device):
+    with _OnDevice(a.device):
         sp = _stream_ptr(stream)
         if block_n is None and cta_group is None and split_k == 1 and max_ctas == 0:
             rc = lib().spork_gemm_sm100_f16f32(M, N, K, pa, pb, pc, variant, sp)
@@ -218,7 +242,7 @@ def matmul_sm100_batched(a, b, c=None, *, variant: int = 0, split_k: int = 1, st
     pa = _dev_ptr(a, torch.float16, "a")
     pb = _dev_ptr(b, torch.float16, "b")
     pc = _dev_ptr(c, torch.float32, "c")
-    with torch.cuda.device(a.device):
+    with _OnDevice(a.device):
         rc = lib().spork_gemm_sm100_f16f32_batched(L, M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
     _check(rc, "spork_gemm_sm100_f16f32_batched")
     return c
@@ -238,7 +262,7 @@ def matmul_sm100_tf32(a, b, c=None, *, variant: int = 0, split_k: int = 1, strea
         raise ValueError(f"c must be {(M, N)}, got {tuple(c.shape)}")
     _same_device(a, b, c)
     pa, pb, pc = (_dev_ptr(t, torch.float32, n) for t, n in ((a, "a"), (b, "b"), (c, "c")))
-    with torch.cuda.device(a.device):
+    with _OnDevice(a.device):
         rc = lib().spork_gemm_sm100_tf32f32(M, N, K, pa, pb, pc, variant, split_k, _stream_ptr(stream))
     _check(rc, "spork_gemm_sm100_tf32f32")
     return c
@@ -325,7 +349,7 @@ def status(stream=None, device=None) -> None:
     """Synchronise ``stream`` and raise SporkError if a kernel reported a device-side timeout."""
     import torch
 
-    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+    with _OnDevice(device if device is not None else torch.cuda.current_device()):
         detail = ctypes.c_uint32(0)
         rc = lib().spork_gemm_sm100_status(_stream_ptr(stream), ctypes.byref(detail))
     if rc != 0:
@@ -356,7 +380,7 @@ def init_test_data(t, code: int, seed: int = 0, transpose_rule: bool = False, st
     import torch
 
     rows, cols = t.shape
-    with torch.cuda.device(t.device):
+    with _OnDevice(t.device):
         rc = lib().spork_init_test_data_f16_at(_dev_ptr(t, torch.float16, "t"), rows, cols, code, seed & 0xFFFFFFFF,
                                                int(transpose_rule), row0, col0, _stream_ptr(stream))
     _check(rc, "spork_init_test_data_f16")
@@ -371,7 +395,7 @@ def gemm_baseline(a, b, c=None, stream=None):
     N, _ = b.shape
     if c is None:
         c = torch.empty((M, N), dtype=torch.float32, device=a.device)
-    with torch.cuda.device(a.device):
+    with _OnDevice(a.device):
         rc = lib().spork_gemm_baseline_f16f32(M, N, K, _dev_ptr(a, torch.float16, "a"), _dev_ptr(b, torch.float16, "b"),
                                               _dev_ptr(c, torch.float32, "c"), _stream_ptr(stream))
     _check(rc, "spork_gemm_baseline_f16f32")
@@ -384,7 +408,7 @@ def compare_f32(x, y, stream=None):
 
     rows, cols = x.shape
     out = torch.empty(2, dtype=torch.int64, device=x.device)
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         rc = lib().spork_compare_f32(_dev_ptr(x, torch.float32, "x"), _dev_ptr(y, torch.float32, "y"), rows, cols,
                                      int(out.data_ptr()), _stream_ptr(stream))
     _check(rc, "spork_compare_f32")
@@ -415,7 +439,7 @@ def attn_fwd(q, k, v, o=None, scale: float | None = None, stream=None, causal: b
     dt = q.dtype
     if dt not in (torch.float16, torch.bfloat16):
         raise TypeError(f"q must be float16 or bfloat16, got {dt}")
-    with torch.cuda.device(q.device):
+    with _OnDevice(q.device):
         rc = lib().spork_attn_sm100_fwd_ex(BH, S, D, _dev_ptr(q, dt, "q"), _dev_ptr(k, dt, "k"), _dev_ptr(v, dt, "v"),
                                            _dev_ptr(o, dt, "o"), ctypes.c_float(scale), int(dt == torch.bfloat16),
                                            int(bool(causal)), _stream_ptr(stream))
